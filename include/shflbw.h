@@ -1,0 +1,246 @@
+/*
+ * shflbw.h -- C ABI of the B200 (sm_100a) Shfl-BW block-sparse inference library.
+ *
+ * Plain C: opaque handles, raw pointers and sizes, int status codes.  No C++ or torch
+ * types cross this boundary.  Every entry point names the interface of the reference
+ * project (hgyhungry/ShflBW_Sparse_NN, paths relative to its root) that it replaces.
+ *
+ * Data conventions (all fp16 arrays are IEEE binary16 passed as uint16_t / void*):
+ *   sparse matrix A: M x K, rows grouped in blocks of V = brow consecutive *stored* rows
+ *     that share one sorted list of non-zero columns (bcol == 1):
+ *       indptr[M/V + 1]   offsets into indices, in non-zero columns
+ *       indices[nnzb]     column ids, ascending inside each row block
+ *       values[nnzb * V]  values[p*V + m] = A_stored[blk*V + m][indices[p]]
+ *       perm[M] or NULL   stored row p is row perm[p] of the result (scatter on store)
+ *   SpMM:   D[perm[i*V+m]][n] = alpha * sum_p values[p][m] * B[indices[p]][n] + beta * C[..][n]
+ *           B: K x N row-major, C/D: M x N row-major, N % 8 == 0.
+ *   SpConv: filter matrix F x (R*S*C), column k = (r*S + s)*C + c; activations NHWC:
+ *           in [B][Hin][Win][C], out [B][Ho][Wo][F], Ho = ceil(Hin/stride), pad R/2, S/2,
+ *           C % 8 == 0.
+ *
+ * Threading: handles are not internally locked.  Exec calls are asynchronous on the
+ * caller's stream and reentrant across distinct states.  The library uses the CUDA
+ * device that is current at the time of each call.
+ */
+#ifndef SHFLBW_H_
+#define SHFLBW_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (replace exit()/assert of block_sparse/cuda_error.h:7-16 and
+ *      block_sparse/spmm/blockwise_op.h:85-87) ---- */
+enum {
+    SHFLBW_OK = 0,
+    SHFLBW_ERR_INVALID_ARG = 1,    /* null pointer, negative size, bad enum              */
+    SHFLBW_ERR_BAD_FORMAT = 2,     /* indptr/indices/perm fail validation, parse error   */
+    SHFLBW_ERR_UNSUPPORTED = 3,    /* shape outside the contract (V, N % 8, C % 8, ...)  */
+    SHFLBW_ERR_CUDA = 4,           /* a CUDA runtime call failed (see shflbw_last_cuda_error) */
+    SHFLBW_ERR_NOT_ON_DEVICE = 5,  /* op init before shflbw_matrix_to_device             */
+    SHFLBW_ERR_DEVICE_TIMEOUT = 6, /* a bounded in-kernel wait gave up (status word set) */
+    SHFLBW_ERR_IO = 7
+};
+
+/* How shflbw_matrix_create_random fills values. */
+enum {
+    SHFLBW_VALUES_INT9_LIBC = 0, /* half(rand() % 9 - 4) from the process-wide libc stream,
+                                    exactly block_sparse/spmm/blockwise_format.h:99-102   */
+    SHFLBW_VALUES_UNIFORM = 1    /* seeded fp16 uniform in [-1, 1): value i of stream s is
+                                    rn_fp16(2*u - 1), u = (splitmix64(s*2^32 + i) >> 40) / 2^24 */
+};
+
+/* Kernel selection for op init. */
+enum {
+    SHFLBW_KERNEL_AUTO = 0,    /* tcgen05/TMEM kernel (the product path)                  */
+    SHFLBW_KERNEL_TCGEN05 = 1,
+    SHFLBW_KERNEL_SIMT = 2     /* plain CUDA-core kernel: bring-up / on-device cross-check */
+};
+
+typedef struct shflbw_matrix shflbw_matrix_t; /* replaces BlockwiseSpMatrix<half> and
+                                                 BlockwiseSpFilter<half>
+                                                 (block_sparse/spmm/blockwise_format.h:13-68,
+                                                  block_sparse/spconv/blockwise_format.h:16-27) */
+
+const char* shflbw_strerror(int status);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* shflbw_last_cuda_error(void);
+/* Library/ABI version, for binding sanity checks. */
+int shflbw_abi_version(void);
+
+/* ---------------------------------------------------------------- format builder ---- */
+
+/* Replaces BlockwiseSpMatrix<half>::init_random (block_sparse/spmm/blockwise_format.h:70-123)
+ * and random_mask (block_sparse/util/random_mask.cc:10-67): mask, permutation, values,
+ * achieved density, config string.  bcol must be 1.  stream seed for UNIFORM values = seed. */
+int shflbw_matrix_create_random(int nrow, int ncol, int brow, int bcol, float density,
+                                int row_permute, unsigned seed, int value_mode,
+                                shflbw_matrix_t** out);
+
+/* Replaces BlockwiseSpFilter<half>::init_random (block_sparse/spconv/blockwise_format.h:29-52):
+ * the F x (R*S*C) matrix plus F, R, S, C and the filter config string. */
+int shflbw_filter_create_random(int F, int R, int S, int C, int brow, int bcol, float density,
+                                int filter_permute, unsigned seed, int value_mode,
+                                shflbw_matrix_t** out);
+
+/* Build from caller arrays (copied).  Replaces filling the public vectors of
+ * BlockwiseSpMatrix (block_sparse/spmm/blockwise_format.h:27-28).  perm may be NULL.
+ * Validates (see shflbw_matrix_validate). */
+int shflbw_matrix_create_from_arrays(int nrow, int ncol, int brow, int nnzb, const int* indptr,
+                                     const int* indices, const uint16_t* values, const int* perm,
+                                     shflbw_matrix_t** out);
+/* Marks a matrix as a conv filter of shape F x R x S x C (nrow == F, ncol == R*S*C). */
+int shflbw_matrix_set_filter_shape(shflbw_matrix_t* m, int F, int R, int S, int C);
+
+/* Replaces BlockwiseSpMatrix<half>::load / ::dump (block_sparse/spmm/blockwise_format.h:151-198,
+ * 125-149; format: example/spmatrix_dump_load.md).  Text is byte-compatible. */
+int shflbw_matrix_load_text(const char* text, size_t len, shflbw_matrix_t** out);
+int shflbw_matrix_load_file(const char* path, shflbw_matrix_t** out);
+/* Writes at most cap bytes; *needed receives the full size (call with buf=NULL to size). */
+int shflbw_matrix_dump_text(const shflbw_matrix_t* m, char* buf, size_t cap, size_t* needed);
+int shflbw_matrix_dump_file(const shflbw_matrix_t* m, const char* path);
+
+/* Structural checks the reference leaves to the caller: indptr monotone from 0 to nnzb,
+ * indices in [0, ncol) and strictly ascending per row block, perm a permutation of [0, nrow). */
+int shflbw_matrix_validate(const shflbw_matrix_t* m);
+
+void shflbw_matrix_destroy(shflbw_matrix_t* m);
+
+/* Scalar getters (public fields of BlockwiseSpMatrix / BlockwiseSpFilter). */
+int shflbw_matrix_nrow(const shflbw_matrix_t* m);
+int shflbw_matrix_ncol(const shflbw_matrix_t* m);
+int shflbw_matrix_nnzb(const shflbw_matrix_t* m);
+int shflbw_matrix_brow(const shflbw_matrix_t* m);
+int shflbw_matrix_bcol(const shflbw_matrix_t* m);
+int shflbw_matrix_row_permute(const shflbw_matrix_t* m);
+unsigned shflbw_matrix_seed(const shflbw_matrix_t* m);
+float shflbw_matrix_density(const shflbw_matrix_t* m);
+const char* shflbw_matrix_config_str(const shflbw_matrix_t* m);
+int shflbw_matrix_filter_shape(const shflbw_matrix_t* m, int* F, int* R, int* S, int* C);
+/* Array getters: pointers into the handle, valid until it is destroyed or rebuilt. */
+const int* shflbw_matrix_indptr(const shflbw_matrix_t* m);        /* nrow/brow + 1 */
+const int* shflbw_matrix_indices(const shflbw_matrix_t* m);       /* nnzb          */
+const uint16_t* shflbw_matrix_values(const shflbw_matrix_t* m);   /* nnzb * brow   */
+const int* shflbw_matrix_row_permute_ids(const shflbw_matrix_t* m); /* nrow or NULL */
+
+/* Replaces BlockwiseSpMatrix<half>::transform_and_sync_device
+ * (block_sparse/spmm/blockwise_format.h:200-266).  Builds the host images and uploads them
+ * to the current device.  Two images are kept:
+ *   - the reference-compatible int32 meta image [indptr | indices*bcol | perm], each section
+ *     zero-padded to 8 ints (readable with shflbw_matrix_meta_image), and
+ *   - the kernel image: every row block's column list padded to a multiple of 16 (extra
+ *     columns repeat the block's last column id and carry zero values), so kernels never
+ *     see a ragged K tail.
+ * Idempotent; rebuilding the matrix drops the device copy. */
+int shflbw_matrix_to_device(shflbw_matrix_t* m);
+int shflbw_matrix_on_device(const shflbw_matrix_t* m);
+/* Host copy of the reference-compatible meta image; *n_int32 = its length. */
+const int* shflbw_matrix_meta_image(const shflbw_matrix_t* m, size_t* n_int32);
+
+/* ------------------------------------------------------------------------- SpMM ---- */
+
+/* Replaces SpmmBlockwiseOpState (block_sparse/spmm/blockwise_op.h:6-17): a POD the caller
+ * may copy.  Holds non-owning device pointers: the matrix handle and B, C, D must outlive it. */
+typedef struct shflbw_spmm_state {
+    int M, N, K, V;
+    int num_row_blocks;
+    int kernel;              /* SHFLBW_KERNEL_* actually selected */
+    int tokens_per_cta;      /* dense-dimension tile of one CTA */
+    int stages;
+    unsigned grid_x, grid_y, block_x;
+    size_t shared_mem_size;
+    int init_success;        /* initSuccess of the reference state */
+    float alpha, beta;
+    const void* B;
+    const void* C;
+    void* D;
+    const int* blk_ptr;      /* padded row-block offsets (units: rows of 16-padded panels) */
+    const int* blk_idx;      /* padded column ids */
+    const void* blk_val;     /* padded fp16 value panels, [rows][V] */
+    const int* perm;         /* device row permutation or NULL */
+    int* status_word;        /* device int: 0 ok, else a SHFLBW_DEVSTAT_* code */
+} shflbw_spmm_state_t;
+
+/* Replaces SpmmBlockwiseOp::initialize / SpmmBlockwiseInitFn
+ * (block_sparse/spmm/blockwise_op.h:73-132, 180-194).  B, C, D are device pointers;
+ * C may be NULL when beta == 0.  alpha is honoured (the reference hard-wires 1.0,
+ * block_sparse/spmm/blockwise_op.h:91-95).  kernel = SHFLBW_KERNEL_*. */
+int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha, const void* C,
+                     float beta, void* D, int kernel, shflbw_spmm_state_t* out);
+
+/* Replaces SpmmBlockwiseOp::operator() / SpmmBlockwiseExecFn
+ * (block_sparse/spmm/blockwise_op.h:169-174, 204-209): asynchronous launch on `stream`
+ * (a cudaStream_t; NULL = default stream).  Returns launch errors only. */
+int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream);
+
+/* Reads (and clears) the device status word of the matrix used by `st`; synchronises the
+ * device.  SHFLBW_OK or SHFLBW_ERR_DEVICE_TIMEOUT. */
+int shflbw_matrix_device_status(const shflbw_matrix_t* m);
+
+/* End-to-end call with HOST buffers (what a plugin caller without device memory uses):
+ * copies B (and C) to the device, runs, copies D back, synchronises.  B/C/D are host
+ * pointers (pinned memory recommended).  Reuses device staging buffers owned by the matrix
+ * handle across calls. */
+int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
+                     const void* C_host, float beta, void* D_host);
+
+/* ----------------------------------------------------------------------- SpConv ---- */
+
+/* Replaces SpconvBlockwiseOpState (block_sparse/spconv/blockwise_op.h:6-17). */
+typedef struct shflbw_spconv_state {
+    int B, Hin, Win, C, F, R, S, stride, Ho, Wo, V;
+    int Bp;                  /* batch rounded up to 8: innermost extent of the staged input */
+    int kernel;
+    int tokens_per_cta;
+    int stages;
+    unsigned grid_x, grid_y, block_x;
+    size_t shared_mem_size;
+    int init_success;
+    float alpha;
+    const void* ifmap;       /* NHWC input (device)  */
+    void* ofmap;             /* NHWC output (device) */
+    void* staged_in;         /* scratch: input re-laid as [C][Hin][Win][Bp]            */
+    void* staged_out;        /* scratch: [B*Ho*Wo][F] in stored filter order, or NULL  */
+    size_t staged_in_bytes, staged_out_bytes;
+    const int* blk_ptr;
+    const int* blk_idx;
+    const void* blk_val;
+    const int* perm;
+    int* status_word;
+} shflbw_spconv_state_t;
+
+/* Replaces SpconvBlockwiseOp::initialize / SpconvBlockwiseInitFn
+ * (block_sparse/spconv/blockwise_op.h:70-131, 161-167).  ifmap/ofmap are NHWC device
+ * pointers.  Scratch for the staged input (and, with a filter permutation, the staged
+ * output) is allocated once per (matrix, shape) and owned by the matrix handle. */
+int shflbw_spconv_init(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
+                       const void* ifmap_nhwc, void* ofmap_nhwc, float alpha, int kernel,
+                       shflbw_spconv_state_t* out);
+
+/* Replaces SpconvBlockwiseOp::operator() / SpconvBlockwiseExecFn
+ * (block_sparse/spconv/blockwise_op.h:148-153, 177-187). */
+int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream);
+
+/* End-to-end conv with HOST NHWC buffers. */
+int shflbw_spconv_host(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
+                       const void* ifmap_host, void* ofmap_host, float alpha);
+
+/* Number of kernel launches one exec call issues (for launch accounting). */
+int shflbw_spmm_launches_per_exec(const shflbw_spmm_state_t* st);
+int shflbw_spconv_launches_per_exec(const shflbw_spconv_state_t* st);
+
+/* Device status word values written by kernels when a bounded wait gives up. */
+enum {
+    SHFLBW_DEVSTAT_OK = 0,
+    SHFLBW_DEVSTAT_TIMEOUT_FULL = 1,   /* consumer never saw a filled stage  */
+    SHFLBW_DEVSTAT_TIMEOUT_EMPTY = 2,  /* producer never saw a freed stage   */
+    SHFLBW_DEVSTAT_TIMEOUT_ACCUM = 3   /* epilogue never saw the accumulator */
+};
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* SHFLBW_H_ */

@@ -1,0 +1,18 @@
+"""B200-native (sm_100a) Shfl-BW block-sparse inference: format builder, SpMM, SpConv.
+
+The compute path is the CUDA library `libshflbw_b200.so` (built in-tree by
+`shflbw_sparse_nn_b200.build`); this package is the thin host-side mirror of the reference's
+operator interface over that library's C ABI (include/shflbw.h).
+"""
+from ._cabi import (KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05, VALUES_INT9_LIBC, VALUES_UNIFORM,
+                    ShflbwError)
+from .blockwise import (BlockwiseSpFilter, BlockwiseSpMatrix, SpconvBlockwiseExecFn,
+                        SpconvBlockwiseInitFn, SpconvBlockwiseOp, SpmmBlockwiseExecFn,
+                        SpmmBlockwiseInitFn, SpmmBlockwiseOp, spconv_host, spmm_host, uniform_half)
+
+__all__ = [
+    "BlockwiseSpMatrix", "BlockwiseSpFilter", "SpmmBlockwiseOp", "SpmmBlockwiseInitFn",
+    "SpmmBlockwiseExecFn", "SpconvBlockwiseOp", "SpconvBlockwiseInitFn", "SpconvBlockwiseExecFn",
+    "spmm_host", "spconv_host", "uniform_half", "ShflbwError",
+    "KERNEL_AUTO", "KERNEL_TCGEN05", "KERNEL_SIMT", "VALUES_INT9_LIBC", "VALUES_UNIFORM",
+]

@@ -1,0 +1,65 @@
+"""In-tree build of the native library (nvcc, sm_100a only).
+
+`python -m shflbw_sparse_nn_b200.build` or `build_library()` compiles
+`csrc/shflbw_capi.cu` + `csrc/shflbw_format.cc` into `libshflbw_b200.so` next to this file.
+nvcc cross-compiles without a GPU.  The shared object is git-ignored; it is a build product.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+PKG_DIR = Path(__file__).resolve().parent
+REPO_ROOT = PKG_DIR.parent
+LIB_PATH = PKG_DIR / "libshflbw_b200.so"
+SOURCES = [PKG_DIR / "csrc" / "shflbw_capi.cu", PKG_DIR / "csrc" / "shflbw_format.cc"]
+HEADERS = [
+    PKG_DIR / "csrc" / "panel_umma.cuh",
+    PKG_DIR / "csrc" / "aux_kernels.cuh",
+    PKG_DIR / "csrc" / "sm100_ptx.cuh",
+    PKG_DIR / "csrc" / "shflbw_internal.hpp",
+    REPO_ROOT / "include" / "shflbw.h",
+]
+
+
+def _nvcc() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; set NVCC=/path/to/nvcc")
+    return cand
+
+
+def needs_build() -> bool:
+    if not LIB_PATH.exists():
+        return True
+    built = LIB_PATH.stat().st_mtime
+    return any(p.stat().st_mtime > built for p in SOURCES + HEADERS)
+
+
+def build_library(force: bool = False, verbose: bool = False) -> Path:
+    """Compile the library if sources are newer than the binary. Returns its path."""
+    if not force and not needs_build():
+        return LIB_PATH
+    cmd = [
+        _nvcc(), "-ccbin", "g++", "-O3", "-std=c++17",
+        "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+        "-Xcompiler", "-fPIC", "-shared",
+        "-I", str(REPO_ROOT / "include"),
+        "-o", str(LIB_PATH),
+    ] + [str(s) for s in SOURCES]
+    if verbose:
+        cmd.insert(1, "-Xptxas=-v")
+        print(" ".join(cmd), file=sys.stderr)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        print(res.stderr, file=sys.stderr)
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -1,0 +1,367 @@
+// CUDA side of the C ABI: device upload of the Shfl-BW images, op init / exec for SpMM and
+// SpConv, and the end-to-end host-buffer calls.  Host code here only validates, fills POD
+// states and launches; all arithmetic happens in the kernels of panel_umma.cuh /
+// aux_kernels.cuh.  There is no CPU fallback: without a CUDA device every op entry point
+// returns SHFLBW_ERR_CUDA.
+//
+// Reference host code this replaces (paths relative to the reference project):
+//   block_sparse/spmm/blockwise_format.h:200-266   transform_and_sync_device
+//   block_sparse/spmm/blockwise_op.h:73-132, 169-209   initialize / operator() / InitFn / ExecFn
+//   block_sparse/spconv/blockwise_op.h:70-131, 148-187
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+
+#include "aux_kernels.cuh"
+#include "panel_umma.cuh"
+#include "shflbw_internal.hpp"
+
+namespace {
+
+thread_local char g_cuda_err[256] = "";
+
+bool cuda_ok(cudaError_t e, const char* what) {
+    if (e == cudaSuccess) return true;
+    snprintf(g_cuda_err, sizeof g_cuda_err, "%s: %s", what, cudaGetErrorString(e));
+    (void)cudaGetLastError();  // clear the sticky-free error state
+    return false;
+}
+#define CK(call) do { if (!cuda_ok((call), #call)) return SHFLBW_ERR_CUDA; } while (0)
+
+int ensure_buffer(void** buf, size_t* have, size_t need) {
+    if (*have >= need && *buf) return SHFLBW_OK;
+    if (*buf) { cudaFree(*buf); *buf = nullptr; *have = 0; }
+    CK(cudaMalloc(buf, need));
+    *have = need;
+    return SHFLBW_OK;
+}
+
+// ---- kernel table -------------------------------------------------------------------
+using PanelKernel = void (*)(const shflbw::PanelParams);
+struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; };
+
+template <int V, int TM, int STAGES, bool CONV>
+PanelChoice choice() {
+    return {shflbw::panel_umma_kernel<V, TM, STAGES, CONV>, (size_t)shflbw::PanelCfg<V, TM, STAGES>::SMEM_BYTES,
+            shflbw::PanelCfg<V, TM, STAGES>::T, STAGES};
+}
+
+// Tile selection.  tokens-per-CTA 256 halves the value-panel traffic per token and is the
+// default; 128 is used when the dense extent is too small to fill the GPU with 256.
+// SHFLBW_TILE=128|256 overrides (tuning aid).
+template <bool CONV>
+int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
+    int tile = 256;
+    const long long ctas256 = ((n_tokens + 255) / 256) * row_blocks;
+    if (ctas256 < 148 * 2) tile = 128;
+    if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
+    switch (V) {
+        case 32:  *out = tile == 256 ? choice<32, 2, 4, CONV>() : choice<32, 1, 4, CONV>(); break;
+        case 64:  *out = tile == 256 ? choice<64, 2, 4, CONV>() : choice<64, 1, 4, CONV>(); break;
+        case 128: *out = tile == 256 ? choice<128, 2, 4, CONV>() : choice<128, 1, 4, CONV>(); break;
+        default: return SHFLBW_ERR_UNSUPPORTED;
+    }
+    if (out->smem > 48 * 1024) {
+        CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
+    }
+    return SHFLBW_OK;
+}
+
+int check_kernel_arg(int kernel) {
+    return (kernel == SHFLBW_KERNEL_AUTO || kernel == SHFLBW_KERNEL_TCGEN05 || kernel == SHFLBW_KERNEL_SIMT)
+               ? SHFLBW_OK : SHFLBW_ERR_INVALID_ARG;
+}
+
+}  // namespace
+
+namespace shflbw {
+void drop_device_copy(shflbw_matrix& m) {
+    void** bufs[] = {&m.d_meta, &m.d_val, &m.stage_in, &m.stage_c, &m.stage_out, &m.conv_in, &m.conv_out};
+    for (void** b : bufs) if (*b) { cudaFree(*b); *b = nullptr; }
+    m.stage_in_bytes = m.stage_c_bytes = m.stage_out_bytes = m.conv_in_bytes = m.conv_out_bytes = 0;
+    m.d_kptr = m.d_kidx = m.d_perm = nullptr;
+    m.d_status = nullptr;
+    m.device = -1;
+}
+}  // namespace shflbw
+
+extern "C" {
+
+const char* shflbw_last_cuda_error(void) { return g_cuda_err; }
+
+int shflbw_matrix_to_device(shflbw_matrix_t* m) {
+    if (!m) return SHFLBW_ERR_INVALID_ARG;
+    if (m->d_meta) return SHFLBW_OK;
+    int rc = shflbw::validate(*m);
+    if (rc != SHFLBW_OK) return rc;
+    shflbw::build_host_images(*m);
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    auto up8 = [](size_t v) { return (v + 7) / 8 * 8; };
+    const size_t o_ptr = 0, o_idx = up8(m->kptr.size()), o_perm = o_idx + up8(m->kidx.size()),
+                 o_stat = o_perm + up8(m->row_permute_ids.size()), total = o_stat + 8;
+    std::vector<int> img(total, 0);
+    std::copy(m->kptr.begin(), m->kptr.end(), img.begin() + o_ptr);
+    std::copy(m->kidx.begin(), m->kidx.end(), img.begin() + o_idx);
+    std::copy(m->row_permute_ids.begin(), m->row_permute_ids.end(), img.begin() + o_perm);
+    CK(cudaMalloc(&m->d_meta, total * sizeof(int)));
+    if (!cuda_ok(cudaMalloc(&m->d_val, m->kval.size() * 2), "cudaMalloc(values)")) {
+        cudaFree(m->d_meta); m->d_meta = nullptr;
+        return SHFLBW_ERR_CUDA;
+    }
+    CK(cudaMemcpy(m->d_meta, img.data(), total * sizeof(int), cudaMemcpyHostToDevice));
+    CK(cudaMemcpy(m->d_val, m->kval.data(), m->kval.size() * 2, cudaMemcpyHostToDevice));
+    const int* base = (const int*)m->d_meta;
+    m->d_kptr = base + o_ptr;
+    m->d_kidx = base + o_idx;
+    m->d_perm = m->row_permute ? base + o_perm : nullptr;
+    m->d_status = (int*)m->d_meta + o_stat;
+    m->device = dev;
+    return SHFLBW_OK;
+}
+
+int shflbw_matrix_on_device(const shflbw_matrix_t* m) { return m && m->d_meta ? 1 : 0; }
+
+int shflbw_matrix_device_status(const shflbw_matrix_t* m) {
+    if (!m || !m->d_status) return SHFLBW_ERR_NOT_ON_DEVICE;
+    int word = 0;
+    CK(cudaDeviceSynchronize());
+    CK(cudaMemcpy(&word, m->d_status, sizeof word, cudaMemcpyDeviceToHost));
+    if (word != 0) {
+        CK(cudaMemset(m->d_status, 0, sizeof word));
+        snprintf(g_cuda_err, sizeof g_cuda_err, "device status word = %d", word);
+        return SHFLBW_ERR_DEVICE_TIMEOUT;
+    }
+    return SHFLBW_OK;
+}
+
+// ------------------------------------------------------------------------------ SpMM --
+
+int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha, const void* C,
+                     float beta, void* D, int kernel, shflbw_spmm_state_t* out) {
+    if (!out) return SHFLBW_ERR_INVALID_ARG;
+    std::memset(out, 0, sizeof *out);
+    if (!m || !B || !D || N <= 0) return SHFLBW_ERR_INVALID_ARG;
+    if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
+    if (beta != 0.f && !C) return SHFLBW_ERR_INVALID_ARG;
+    if (!m->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;           // reference: assert(device_synced)
+    if (m->bcol != 1) return SHFLBW_ERR_UNSUPPORTED;            // reference: assert(bcol == BK)
+    if (m->brow != 32 && m->brow != 64 && m->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    if (N % 8) return SHFLBW_ERR_UNSUPPORTED;                   // 16-byte rows of fp16
+    const uintptr_t al = (uintptr_t)B | (uintptr_t)D | (uintptr_t)C;
+    if (al & 15) return SHFLBW_ERR_UNSUPPORTED;
+
+    out->M = m->nrow; out->N = N; out->K = m->ncol; out->V = m->brow;
+    out->num_row_blocks = m->nrow / m->brow;
+    out->alpha = alpha; out->beta = beta;
+    out->B = B; out->C = C; out->D = D;
+    out->blk_ptr = m->d_kptr; out->blk_idx = m->d_kidx; out->blk_val = m->d_val;
+    out->perm = m->d_perm; out->status_word = m->d_status;
+    if (kernel == SHFLBW_KERNEL_SIMT) {
+        out->kernel = SHFLBW_KERNEL_SIMT;
+        out->block_x = 128; out->grid_x = (N + 127) / 128; out->grid_y = m->nrow;
+        out->tokens_per_cta = 128; out->stages = 0; out->shared_mem_size = 0;
+    } else {
+        PanelChoice ch;
+        int rc = pick_panel<false>(m->brow, N, out->num_row_blocks, &ch);
+        if (rc != SHFLBW_OK) return rc;
+        out->kernel = SHFLBW_KERNEL_TCGEN05;
+        out->tokens_per_cta = ch.tokens; out->stages = ch.stages;
+        out->block_x = shflbw::kPanelThreads;
+        out->grid_x = (N + ch.tokens - 1) / ch.tokens; out->grid_y = out->num_row_blocks;
+        out->shared_mem_size = ch.smem;
+    }
+    out->init_success = 1;
+    return SHFLBW_OK;
+}
+
+int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
+    if (!st || !st->init_success) return SHFLBW_ERR_INVALID_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (st->kernel == SHFLBW_KERNEL_SIMT) {
+        shflbw::simt_spmm<<<dim3(st->grid_x, st->grid_y), st->block_x, 0, s>>>(
+            st->blk_ptr, st->blk_idx, (const __half*)st->blk_val, st->perm, (const __half*)st->B,
+            (const __half*)st->C, (__half*)st->D, st->M, st->N, st->V, st->alpha, st->beta);
+    } else {
+        PanelChoice ch;
+        // Re-derive the function pointer from the recorded tile (the state is a POD and may
+        // have been copied); attribute setting already happened at init.
+        const int tm = st->tokens_per_cta / 128;
+        switch (st->V * 10 + tm) {
+            case 321: ch = choice<32, 1, 4, false>(); break;
+            case 322: ch = choice<32, 2, 4, false>(); break;
+            case 641: ch = choice<64, 1, 4, false>(); break;
+            case 642: ch = choice<64, 2, 4, false>(); break;
+            case 1281: ch = choice<128, 1, 4, false>(); break;
+            case 1282: ch = choice<128, 2, 4, false>(); break;
+            default: return SHFLBW_ERR_INVALID_ARG;
+        }
+        shflbw::PanelParams p{};
+        p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
+        p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
+        p.B = (const __half*)st->B; p.C = (const __half*)st->C; p.D = (__half*)st->D; p.N = st->N;
+        ch.fn<<<dim3(st->grid_x, st->grid_y), st->block_x, st->shared_mem_size, s>>>(p);
+    }
+    CK(cudaGetLastError());
+    return SHFLBW_OK;
+}
+
+int shflbw_spmm_launches_per_exec(const shflbw_spmm_state_t* st) { return st && st->init_success ? 1 : 0; }
+
+int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha, const void* C_host,
+                     float beta, void* D_host) {
+    if (!m || !B_host || !D_host || N <= 0) return SHFLBW_ERR_INVALID_ARG;
+    if (beta != 0.f && !C_host) return SHFLBW_ERR_INVALID_ARG;
+    int rc = shflbw_matrix_to_device(m);
+    if (rc != SHFLBW_OK) return rc;
+    const size_t bB = (size_t)m->ncol * N * 2, bD = (size_t)m->nrow * N * 2;
+    if ((rc = ensure_buffer(&m->stage_in, &m->stage_in_bytes, bB)) != SHFLBW_OK) return rc;
+    if ((rc = ensure_buffer(&m->stage_out, &m->stage_out_bytes, bD)) != SHFLBW_OK) return rc;
+    if (beta != 0.f && (rc = ensure_buffer(&m->stage_c, &m->stage_c_bytes, bD)) != SHFLBW_OK) return rc;
+    CK(cudaMemcpyAsync(m->stage_in, B_host, bB, cudaMemcpyHostToDevice, 0));
+    if (beta != 0.f) CK(cudaMemcpyAsync(m->stage_c, C_host, bD, cudaMemcpyHostToDevice, 0));
+    shflbw_spmm_state_t st;
+    rc = shflbw_spmm_init(m, N, m->stage_in, alpha, beta != 0.f ? m->stage_c : nullptr, beta, m->stage_out,
+                          SHFLBW_KERNEL_AUTO, &st);
+    if (rc != SHFLBW_OK) return rc;
+    if ((rc = shflbw_spmm_exec(&st, 0)) != SHFLBW_OK) return rc;
+    CK(cudaMemcpyAsync(D_host, m->stage_out, bD, cudaMemcpyDeviceToHost, 0));
+    CK(cudaStreamSynchronize(0));
+    return SHFLBW_OK;
+}
+
+// ---------------------------------------------------------------------------- SpConv --
+
+int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap,
+                       void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
+    if (!out) return SHFLBW_ERR_INVALID_ARG;
+    std::memset(out, 0, sizeof *out);
+    if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
+    if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
+    if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
+    if (!f->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+    if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
+    if (((uintptr_t)ifmap | (uintptr_t)ofmap) & 15) return SHFLBW_ERR_UNSUPPORTED;
+    const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
+    const int Bp = (B + 7) / 8 * 8;
+    const long long tokens = (long long)Ho * Wo * Bp;
+    if ((long long)f->C * Hin * Win >= (1ll << 31) / 1 || tokens >= (1ll << 31) ||
+        (long long)f->C * Hin * Win * Bp >= (1ll << 40))
+        return SHFLBW_ERR_UNSUPPORTED;
+
+    out->B = B; out->Hin = Hin; out->Win = Win; out->C = f->C; out->F = f->F; out->R = f->R; out->S = f->S;
+    out->stride = stride; out->Ho = Ho; out->Wo = Wo; out->V = f->brow; out->Bp = Bp;
+    out->alpha = alpha; out->ifmap = ifmap; out->ofmap = ofmap;
+    out->blk_ptr = f->d_kptr; out->blk_idx = f->d_kidx; out->blk_val = f->d_val;
+    out->perm = f->d_perm; out->status_word = f->d_status;
+    if (kernel == SHFLBW_KERNEL_SIMT) {
+        out->kernel = SHFLBW_KERNEL_SIMT;
+        out->block_x = 128; out->grid_x = (f->F + 127) / 128; out->grid_y = (unsigned)(B * Ho * Wo);
+        out->init_success = 1;
+        return SHFLBW_OK;
+    }
+    PanelChoice ch;
+    int rc = pick_panel<true>(f->brow, tokens, f->F / f->brow, &ch);
+    if (rc != SHFLBW_OK) return rc;
+    out->kernel = SHFLBW_KERNEL_TCGEN05;
+    out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->block_x = shflbw::kPanelThreads;
+    out->grid_x = (unsigned)((tokens + ch.tokens - 1) / ch.tokens); out->grid_y = f->F / f->brow;
+    out->shared_mem_size = ch.smem;
+    // Scratch owned by the filter handle, grown on demand.
+    out->staged_in_bytes = (size_t)f->C * Hin * Win * Bp * 2;
+    if ((rc = ensure_buffer(&f->conv_in, &f->conv_in_bytes, out->staged_in_bytes)) != SHFLBW_OK) return rc;
+    out->staged_in = f->conv_in;
+    if (f->row_permute) {
+        out->staged_out_bytes = (size_t)B * Ho * Wo * f->F * 2;
+        if ((rc = ensure_buffer(&f->conv_out, &f->conv_out_bytes, out->staged_out_bytes)) != SHFLBW_OK) return rc;
+        out->staged_out = f->conv_out;
+        if ((size_t)f->F * 16 > 48 * 1024)
+            CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, f->F * 16));
+    }
+    out->init_success = 1;
+    return SHFLBW_OK;
+}
+
+int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
+    if (!st || !st->init_success) return SHFLBW_ERR_INVALID_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (st->kernel == SHFLBW_KERNEL_SIMT) {
+        shflbw::simt_spconv<<<dim3(st->grid_x, st->grid_y), st->block_x, 0, s>>>(
+            st->blk_ptr, st->blk_idx, (const __half*)st->blk_val, st->perm, (const __half*)st->ifmap,
+            (__half*)st->ofmap, st->B, st->Hin, st->Win, st->C, st->F, st->R, st->S, st->stride, st->Ho,
+            st->Wo, st->V, st->alpha);
+        CK(cudaGetLastError());
+        return SHFLBW_OK;
+    }
+    PanelChoice ch;
+    const int tm = st->tokens_per_cta / 128;
+    switch (st->V * 10 + tm) {
+        case 321: ch = choice<32, 1, 4, true>(); break;
+        case 322: ch = choice<32, 2, 4, true>(); break;
+        case 641: ch = choice<64, 1, 4, true>(); break;
+        case 642: ch = choice<64, 2, 4, true>(); break;
+        case 1281: ch = choice<128, 1, 4, true>(); break;
+        case 1282: ch = choice<128, 2, 4, true>(); break;
+        default: return SHFLBW_ERR_INVALID_ARG;
+    }
+    // 1. NHWC -> channel-major, batch-innermost staging.
+    {
+        const int P = st->Hin * st->Win;
+        const int NT = st->Bp < 32 ? st->Bp : 32, PT = shflbw::kRelayoutSlots / NT;
+        const int n_tiles = (st->Bp + NT - 1) / NT;
+        dim3 grid((unsigned)(((P + PT - 1) / PT) * n_tiles), (unsigned)((st->C + shflbw::kRelayoutC - 1) / shflbw::kRelayoutC));
+        shflbw::relayout_nhwc_to_chwn<<<grid, 256, 0, s>>>((const __half*)st->ifmap, (__half*)st->staged_in,
+                                                           st->B, st->Bp, P, st->C);
+    }
+    // 2. implicit-GEMM panel kernel.
+    shflbw::PanelParams p{};
+    p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
+    p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = 0.f;
+    p.N = st->Ho * st->Wo * st->Bp;
+    p.Xs = (const __half*)st->staged_in;
+    p.out = (__half*)(st->staged_out ? st->staged_out : st->ofmap);
+    p.Bn = st->B; p.Bp = st->Bp; p.Hin = st->Hin; p.Win = st->Win; p.Cin = st->C; p.F = st->F;
+    p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
+    ch.fn<<<dim3(st->grid_x, st->grid_y), st->block_x, st->shared_mem_size, s>>>(p);
+    // 3. inverse filter permutation.
+    if (st->staged_out) {
+        const int num_pos = st->B * st->Ho * st->Wo;
+        int blocks = (num_pos + 7) / 8;
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        shflbw::unpermute_filters<<<blocks, 256, (size_t)st->F * 16, s>>>(
+            (const __half*)st->staged_out, (__half*)st->ofmap, st->perm, num_pos, st->F);
+    }
+    CK(cudaGetLastError());
+    return SHFLBW_OK;
+}
+
+int shflbw_spconv_launches_per_exec(const shflbw_spconv_state_t* st) {
+    if (!st || !st->init_success) return 0;
+    if (st->kernel == SHFLBW_KERNEL_SIMT) return 1;
+    return st->staged_out ? 3 : 2;
+}
+
+int shflbw_spconv_host(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap_host,
+                       void* ofmap_host, float alpha) {
+    if (!f || !ifmap_host || !ofmap_host || !f->is_filter || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0)
+        return SHFLBW_ERR_INVALID_ARG;
+    int rc = shflbw_matrix_to_device(f);
+    if (rc != SHFLBW_OK) return rc;
+    const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
+    const size_t bI = (size_t)B * Hin * Win * f->C * 2, bO = (size_t)B * Ho * Wo * f->F * 2;
+    if ((rc = ensure_buffer(&f->stage_in, &f->stage_in_bytes, bI)) != SHFLBW_OK) return rc;
+    if ((rc = ensure_buffer(&f->stage_out, &f->stage_out_bytes, bO)) != SHFLBW_OK) return rc;
+    CK(cudaMemcpyAsync(f->stage_in, ifmap_host, bI, cudaMemcpyHostToDevice, 0));
+    shflbw_spconv_state_t st;
+    rc = shflbw_spconv_init(f, B, Hin, Win, stride, f->stage_in, f->stage_out, alpha, SHFLBW_KERNEL_AUTO, &st);
+    if (rc != SHFLBW_OK) return rc;
+    if ((rc = shflbw_spconv_exec(&st, 0)) != SHFLBW_OK) return rc;
+    CK(cudaMemcpyAsync(ofmap_host, f->stage_out, bO, cudaMemcpyDeviceToHost, 0));
+    CK(cudaStreamSynchronize(0));
+    return SHFLBW_OK;
+}
+
+}  // extern "C"
