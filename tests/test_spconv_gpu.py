@@ -1,0 +1,113 @@
+"""SpConv parity on the GPU (NHWC in / NHWC out) through the C ABI, against the CPU oracle,
+the committed reference fixtures (reference layouts, transposed here: pure data movement)
+and the reference's own CUDA kernel.  Same tolerance as SpMM: max(1e-2*|ref|, 1e-3)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_api as oa
+import shflbw_sparse_nn_b200 as sb
+from conftest import assert_close_fp16
+from gpu_util import dev, host, run_spconv
+
+pytestmark = pytest.mark.gpu
+
+
+def _arrays(f):
+    return f.indptr, f.indices, f.values, (f.row_permute_ids if f.row_permute else None)
+
+
+def _oracle(f, Bn, Hin, Win, stride, x, alpha=1.0):
+    indptr, indices, values, perm = _arrays(f)
+    return oa.spconv_ref_nhwc(Bn, Hin, Win, f.C, f.F, f.R, f.S, stride, f.brow, indptr, indices, values, perm, x, alpha)
+
+
+def test_reference_fixture_outputs(golden_dir):
+    z = np.load(golden_dir / "spconv_cases.npz")
+    for i in range(int(z["n_cases"])):
+        Bn, H, W, Cc, F, R, S, st, V, perm, seed = (int(v) for v in z[f"v{i}_args"])
+        indices = z[f"v{i}_indices"]
+        f = sb.BlockwiseSpFilter.from_arrays(F, R, S, Cc, V, z[f"v{i}_indptr"], indices,
+                                             sb.uniform_half(seed, indices.size * V), z[f"v{i}_perm"] if perm else None)
+        x_chwn = sb.uniform_half(seed + 1000, Cc * H * W * Bn).reshape(Cc, H, W, Bn)
+        x = np.ascontiguousarray(x_chwn.transpose(3, 1, 2, 0))
+        O, _ = run_spconv(f, Bn, H, W, st, x)
+        ref = z[f"v{i}_O"].transpose(3, 1, 2, 0)[:, : O.shape[1], : O.shape[2], :]
+        assert_close_fp16(O, ref, what=f"conv fixture {i}")
+
+
+@pytest.mark.parametrize("V", [32, 64, 128])
+@pytest.mark.parametrize("permute", [False, True])
+@pytest.mark.parametrize("stride", [1, 2])
+def test_3x3_small(V, permute, stride):
+    Bn, H, W, Cc, F = 8, 9, 7, 32, 2 * V
+    f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, V, 1, 0.2, permute, 5 + V, values="uniform")
+    x = sb.uniform_half(77, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    O, op = run_spconv(f, Bn, H, W, stride, x)
+    assert op.launches_per_exec == (3 if permute else 2)
+    assert_close_fp16(O, _oracle(f, Bn, H, W, stride, x), what=f"3x3 V={V} perm={permute} stride={stride}")
+
+
+@pytest.mark.parametrize("Bn", [1, 2, 5, 16, 24, 40])
+def test_batch_not_multiple_of_8_and_1x1(Bn):
+    f = sb.BlockwiseSpFilter().init_random(128, 1, 1, 64, 64, 1, 0.25, True, 9, values="uniform")
+    x = sb.uniform_half(78 + Bn, Bn * 6 * 5 * 64).reshape(Bn, 6, 5, 64)
+    O, _ = run_spconv(f, Bn, 6, 5, 1, x, alpha=0.25)
+    assert_close_fp16(O, _oracle(f, Bn, 6, 5, 1, x, 0.25), what=f"1x1 batch {Bn}")
+
+
+@pytest.mark.parametrize("tokens", [128, 256])
+def test_reference_test_shape_int9(tokens):
+    """The reference's conv test case (n,h,w,c,f,r,s,stride) = (128,14,14,256,256,3,3,1), d=0.1,
+    seed 2021, integer inputs, its exact acceptance rule; run at batch 16 to bound CPU time,
+    and with the filter permutation ON (the reference never tests that path)."""
+    ctypes.CDLL(None).srand(3)
+    f = sb.BlockwiseSpFilter().init_random(256, 3, 3, 256, 64, 1, 0.1, True, 2021, values="int9")
+    x = np.random.default_rng(5).integers(-4, 5, (16, 14, 14, 256)).astype(np.float16)
+    O, op = run_spconv(f, 16, 14, 14, 1, x, tokens=tokens)
+    assert op._state.tokens_per_cta == tokens
+    assert oa.ref_rule_violations(O, _oracle(f, 16, 14, 14, 1, x)) == 0
+
+
+def test_simt_cross_check_kernel_matches_oracle():
+    f = sb.BlockwiseSpFilter().init_random(64, 3, 3, 16, 32, 1, 0.3, True, 2, values="uniform")
+    x = sb.uniform_half(3, 4 * 6 * 6 * 16).reshape(4, 6, 6, 16)
+    O, _ = run_spconv(f, 4, 6, 6, 2, x, kernel=sb.KERNEL_SIMT)
+    assert_close_fp16(O, _oracle(f, 4, 6, 6, 2, x), what="simt conv")
+
+
+def test_headline_16x14x14x512_to_2048():
+    """BASELINE config 3 at full size."""
+    Bn, H, W, Cc, F, V = 16, 14, 14, 512, 2048, 64
+    f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, V, 1, 0.1, True, 2021, values="uniform")
+    assert f.nnzb == 14746
+    x = sb.uniform_half(8, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    O, op = run_spconv(f, Bn, H, W, 1, x)
+    O2, _ = run_spconv(f, Bn, H, W, 1, x)
+    assert np.array_equal(O.view(np.uint16), O2.view(np.uint16))          # deterministic
+    indptr, indices, values, perm = _arrays(f)
+    f_np = sb.BlockwiseSpFilter.from_arrays(F, 3, 3, Cc, V, indptr, indices, values, None)
+    O_np, _ = run_spconv(f_np, Bn, H, W, 1, x)
+    assert np.array_equal(O[..., perm].view(np.uint16), O_np.view(np.uint16))  # permutation = pure scatter
+    assert_close_fp16(O, _oracle(f, Bn, H, W, 1, x), what="config 3 vs oracle")
+    O_simt, _ = run_spconv(f, Bn, H, W, 1, x, kernel=sb.KERNEL_SIMT)
+    assert_close_fp16(O, O_simt.astype(np.float32), what="config 3 vs simt")
+    if oa.ref_gpu() is not None:
+        # reference kernel: input [C][H][W][B], output [F][H][W][B]
+        xd = dev(np.ascontiguousarray(x.transpose(3, 1, 2, 0)))
+        od = torch.zeros((F, H, W, Bn), dtype=torch.float16, device="cuda")
+        cfg = oa.ref_gpu_conv_configs(V)[0][0]
+        rc, _ = oa.ref_gpu_spconv(cfg, Bn, H, W, Cc, F, 3, 3, 1, V, indptr, indices, values, perm, xd.data_ptr(), od.data_ptr())
+        assert rc == 0
+        assert_close_fp16(O, host(od).astype(np.float32).transpose(3, 1, 2, 0), what="config 3 vs reference CUDA kernel")
+
+
+def test_host_buffer_call_equals_device_call():
+    f = sb.BlockwiseSpFilter().init_random(128, 3, 3, 32, 64, 1, 0.2, True, 31, values="uniform")
+    x = sb.uniform_half(32, 8 * 10 * 10 * 32).reshape(8, 10, 10, 32)
+    O_dev, _ = run_spconv(f, 8, 10, 10, 1, x)
+    O_host = np.zeros((8, 10, 10, 128), np.float16)
+    sb.spconv_host(f, 8, 10, 10, 1, x, O_host)
+    assert np.array_equal(O_host.view(np.uint16), O_dev.view(np.uint16))

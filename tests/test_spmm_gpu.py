@@ -1,0 +1,169 @@
+"""SpMM parity on the GPU, through the C ABI, against the CPU oracle, the committed
+reference fixtures and the reference's own CUDA kernels (when oracle/_ref is present).
+
+Tolerance: fp16 inputs/outputs with fp32 accumulation -> |got - ref| <= max(1e-2*|ref|, 1e-3)
+(conftest.assert_close_fp16).  Integer-valued inputs use the reference's own rule
+|ref - d| <= 1e-3*|ref| with no floor, which then means exact."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+import oracle_api as oa
+import shflbw_sparse_nn_b200 as sb
+from conftest import assert_close_fp16
+from gpu_util import dev, host, run_spmm
+
+pytestmark = pytest.mark.gpu
+
+
+def _arrays(m):
+    return m.indptr, m.indices, m.values, (m.row_permute_ids if m.row_permute else None)
+
+
+def _oracle(m, N, B, alpha=1.0, Cm=None, beta=0.0):
+    indptr, indices, values, perm = _arrays(m)
+    return oa.spmm_ref(m.nrow, N, m.brow, indptr, indices, values, perm, B, alpha, Cm, beta)
+
+
+def test_config1_256cubed_v32_uniform():
+    """BASELINE config 1: M=K=N=256, V=32, d=0.1, permuted, uniform[-1,1] values."""
+    m = sb.BlockwiseSpMatrix().init_random(256, 256, 32, 1, 0.1, True, 2021, values="uniform")
+    assert m.nnzb == 205
+    B = sb.uniform_half(3021, 256 * 256).reshape(256, 256)
+    D, op = run_spmm(m, 256, B)
+    assert op._state.kernel == sb.KERNEL_TCGEN05
+    assert_close_fp16(D, _oracle(m, 256, B), what="config 1")
+
+
+def test_config1_int9_reference_rule():
+    ctypes.CDLL(None).srand(1)
+    m = sb.BlockwiseSpMatrix().init_random(256, 256, 32, 1, 0.1, True, 2021, values="int9")
+    rng = np.random.default_rng(1)
+    B = rng.integers(-4, 5, (256, 256)).astype(np.float16)
+    D, _ = run_spmm(m, 256, B)
+    assert oa.ref_rule_violations(D, _oracle(m, 256, B)) == 0
+
+
+def test_reference_fixture_outputs(golden_dir):
+    """Outputs of the reference's own get_host_reference, committed under tests/golden."""
+    z = np.load(golden_dir / "spmm_cases.npz")
+    for i in range(int(z["n_cases"])):
+        M, K, N, V, perm, seed = (int(v) for v in z[f"s{i}_args"])
+        if V not in (32, 64, 128):
+            continue
+        beta = float(z[f"s{i}_beta"])
+        indices = z[f"s{i}_indices"]
+        m = sb.BlockwiseSpMatrix.from_arrays(M, K, V, z[f"s{i}_indptr"], indices, sb.uniform_half(seed, indices.size * V),
+                                             z[f"s{i}_perm"] if perm else None)
+        B = sb.uniform_half(seed + 1000, K * N).reshape(K, N)
+        Cm = sb.uniform_half(seed + 2000, M * N).reshape(M, N) if beta else None
+        D, _ = run_spmm(m, N, B, 1.0, Cm, beta)
+        assert_close_fp16(D, z[f"s{i}_D"], what=f"fixture {i}")
+
+
+@pytest.mark.parametrize("V", [32, 64, 128])
+@pytest.mark.parametrize("permute", [False, True])
+@pytest.mark.parametrize("tokens", [128, 256])
+def test_reference_test_shape_1024x960x1024(V, permute, tokens):
+    """The reference's own test case (m,n,k,d,seed) = (1024,960,1024,0.1,2021), integer inputs,
+    its acceptance rule; N = 960 exercises the dense-dimension residue."""
+    ctypes.CDLL(None).srand(V + permute)
+    m = sb.BlockwiseSpMatrix().init_random(1024, 1024, V, 1, 0.1, permute, 2021, values="int9")
+    B = np.random.default_rng(V).integers(-4, 5, (1024, 960)).astype(np.float16)
+    D, op = run_spmm(m, 960, B, tokens=tokens)
+    assert op._state.tokens_per_cta == tokens
+    assert oa.ref_rule_violations(D, _oracle(m, 960, B)) == 0
+
+
+@pytest.mark.parametrize("V", [32, 64, 128])
+@pytest.mark.parametrize("N", [8, 40, 136, 264, 520])
+def test_dense_residue_and_alpha_beta(V, N):
+    m = sb.BlockwiseSpMatrix().init_random(2 * V, 320, V, 1, 0.3, True, 11 + N, values="uniform")
+    B = sb.uniform_half(50 + N, 320 * N).reshape(320, N)
+    Cm = sb.uniform_half(60 + N, 2 * V * N).reshape(2 * V, N)
+    D, _ = run_spmm(m, N, B, 0.5, Cm, 2.0)
+    assert_close_fp16(D, _oracle(m, N, B, 0.5, Cm, 2.0), what=f"V={V} N={N} alpha/beta")
+    D1, _ = run_spmm(m, N, B)
+    assert_close_fp16(D1, _oracle(m, N, B), what=f"V={V} N={N}")
+
+
+@pytest.mark.parametrize("V", [32, 64, 128])
+def test_ragged_and_empty_row_blocks(V):
+    """Column counts 0, 1, 15, 16, 17, 63, 64, 65, 130 per row block: every K-tail case."""
+    counts = [0, 1, 15, 16, 17, 63, 64, 65, 130]
+    K = 160
+    rng = np.random.default_rng(V)
+    indptr = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    indices = np.concatenate([np.sort(rng.choice(K, c, replace=False)) for c in counts]).astype(np.int32)
+    M = V * len(counts)
+    vals = sb.uniform_half(V, indices.size * V)
+    perm = rng.permutation(M).astype(np.int32)
+    m = sb.BlockwiseSpMatrix.from_arrays(M, K, V, indptr, indices, vals, perm)
+    B = sb.uniform_half(99, K * 72).reshape(K, 72)
+    D, _ = run_spmm(m, 72, B)
+    ref = _oracle(m, 72, B)
+    assert_close_fp16(D, ref, what=f"ragged V={V}")
+    assert np.all(D[perm[:V]] == 0)  # the empty row block writes zeros, not garbage
+
+
+def test_simt_cross_check_kernel_matches_oracle():
+    m = sb.BlockwiseSpMatrix().init_random(256, 256, 64, 1, 0.2, True, 3, values="uniform")
+    B = sb.uniform_half(4, 256 * 96).reshape(256, 96)
+    D, op = run_spmm(m, 96, B, kernel=sb.KERNEL_SIMT)
+    assert op._state.kernel == sb.KERNEL_SIMT
+    assert_close_fp16(D, _oracle(m, 96, B), what="simt")
+
+
+def test_headline_4096cubed_v64_d01():
+    """BASELINE config 2 at full size: permutation/index handling checked exactly through
+    size-independent properties, values against the oracle on a column slice, against the
+    plain CUDA-core kernel on the whole matrix, and against the reference's CUDA kernel."""
+    M = K = N = 4096
+    V = 64
+    m = sb.BlockwiseSpMatrix().init_random(M, K, V, 1, 0.1, True, 2021, values="uniform")
+    assert m.nnzb == 26214
+    B = sb.uniform_half(7, K * N).reshape(K, N)
+    D, op = run_spmm(m, N, B)
+    assert op.launches_per_exec == 1
+    # (a) determinism: bitwise equal on a second run
+    D2, _ = run_spmm(m, N, B)
+    assert np.array_equal(D.view(np.uint16), D2.view(np.uint16))
+    # (b) the inverse permutation is a pure row scatter: same matrix without permutation
+    #     gives bitwise the same rows at the stored positions
+    indptr, indices, values, perm = _arrays(m)
+    m_np = sb.BlockwiseSpMatrix.from_arrays(M, K, V, indptr, indices, values, None)
+    D_np, _ = run_spmm(m_np, N, B)
+    assert np.array_equal(D[perm].view(np.uint16), D_np.view(np.uint16))
+    # (c) oracle on a 64-column slice (columns are independent)
+    cols = slice(1000, 1064)
+    ref = oa.spmm_ref(M, 64, V, indptr, indices, values, perm, np.ascontiguousarray(B[:, cols]))
+    assert_close_fp16(D[:, cols], ref, what="4096^3 slice vs oracle")
+    # (d) whole matrix vs the plain CUDA-core kernel
+    D_simt, _ = run_spmm(m, N, B, kernel=sb.KERNEL_SIMT)
+    assert_close_fp16(D, D_simt.astype(np.float32), what="4096^3 vs simt")
+    # (e) the reference's own CUDA kernel on identical arrays
+    if oa.ref_gpu() is not None:
+        Bd = dev(B)
+        Dd = torch.zeros((M, N), dtype=torch.float16, device="cuda")
+        cfg = oa.ref_gpu_spmm_configs(V)[1][0]
+        rc, _ = oa.ref_gpu_spmm(cfg, M, K, N, V, indptr, indices, values, perm, Bd.data_ptr(), Dd.data_ptr())
+        assert rc == 0
+        assert_close_fp16(D, host(Dd).astype(np.float32), what="4096^3 vs reference CUDA kernel")
+
+
+def test_host_buffer_call_equals_device_call():
+    m = sb.BlockwiseSpMatrix().init_random(512, 384, 64, 1, 0.15, True, 21, values="uniform")
+    B = sb.uniform_half(22, 384 * 200).reshape(384, 200)
+    D_dev, _ = run_spmm(m, 200, B)
+    D_host = np.zeros((512, 200), np.float16)
+    sb.spmm_host(m, 200, B, D_host)
+    assert np.array_equal(D_host.view(np.uint16), D_dev.view(np.uint16))
+
+
+@pytest.mark.skipif(oa.ref_host() is None, reason="oracle/_ref not present")
+def test_meta_image_equals_reference_transform_and_sync_device():
+    r = oa.RefMatrix.init_random(512, 384, 32, 0.15, True, 17)
+    m = sb.BlockwiseSpMatrix.from_arrays(512, 384, 32, r.indptr, r.indices, r.values, r.perm)
+    assert np.array_equal(m.meta_h, r.meta_image())
