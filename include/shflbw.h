@@ -148,8 +148,11 @@ typedef struct shflbw_spmm_state {
     int M, N, K, V;
     int num_row_blocks;
     int kernel;              /* SHFLBW_KERNEL_* actually selected */
-    int tokens_per_cta;      /* dense-dimension tile of one CTA */
-    int stages;
+    int tokens_per_cta;      /* dense-dimension tile of one work item */
+    int stages;              /* shared-memory pipeline depth */
+    int producer_warps;      /* warps issuing the gather */
+    int variant;             /* pipeline-shape variant (0 = default) */
+    int num_items, tiles_n;  /* work items = row blocks x dense tiles */
     unsigned grid_x, grid_y, block_x;
     size_t shared_mem_size;
     int init_success;        /* initSuccess of the reference state */
@@ -196,6 +199,9 @@ typedef struct shflbw_spconv_state {
     int kernel;
     int tokens_per_cta;
     int stages;
+    int producer_warps;
+    int variant;
+    int num_items, tiles_n;
     unsigned grid_x, grid_y, block_x;
     size_t shared_mem_size;
     int init_success;

@@ -28,7 +28,8 @@ class SpmmState(C.Structure):
     _fields_ = [
         ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("V", C.c_int),
         ("num_row_blocks", C.c_int), ("kernel", C.c_int), ("tokens_per_cta", C.c_int),
-        ("stages", C.c_int),
+        ("stages", C.c_int), ("producer_warps", C.c_int), ("variant", C.c_int), ("num_items", C.c_int),
+        ("tiles_n", C.c_int),
         ("grid_x", C.c_uint), ("grid_y", C.c_uint), ("block_x", C.c_uint),
         ("shared_mem_size", C.c_size_t), ("init_success", C.c_int),
         ("alpha", C.c_float), ("beta", C.c_float),
@@ -44,7 +45,8 @@ class SpconvState(C.Structure):
         ("B", C.c_int), ("Hin", C.c_int), ("Win", C.c_int), ("C", C.c_int), ("F", C.c_int),
         ("R", C.c_int), ("S", C.c_int), ("stride", C.c_int), ("Ho", C.c_int), ("Wo", C.c_int),
         ("V", C.c_int), ("Bp", C.c_int), ("kernel", C.c_int), ("tokens_per_cta", C.c_int),
-        ("stages", C.c_int),
+        ("stages", C.c_int), ("producer_warps", C.c_int), ("variant", C.c_int), ("num_items", C.c_int),
+        ("tiles_n", C.c_int),
         ("grid_x", C.c_uint), ("grid_y", C.c_uint), ("block_x", C.c_uint),
         ("shared_mem_size", C.c_size_t), ("init_success", C.c_int), ("alpha", C.c_float),
         ("ifmap", C.c_void_p), ("ofmap", C.c_void_p), ("staged_in", C.c_void_p),

@@ -49,7 +49,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         "-Xcompiler", "-fPIC", "-shared",
         "-I", str(REPO_ROOT / "include"),
         "-o", str(LIB_PATH),
-    ] + [str(s) for s in SOURCES]
+    ] + os.environ.get("SHFLBW_NVCC_FLAGS", "").split() + [str(s) for s in SOURCES]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
         print(" ".join(cmd), file=sys.stderr)

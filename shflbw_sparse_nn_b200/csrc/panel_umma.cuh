@@ -1,22 +1,36 @@
-// The Shfl-BW panel kernel for sm_100a: one CTA computes, for ONE row block of V stored
-// rows and ONE tile of T = 128*TM dense columns ("tokens": SpMM columns of B, or SpConv
-// output positions), the dense contraction
+// The Shfl-BW panel kernel for sm_100a (persistent, warp-specialised).
+//
+// Work item = ONE row block of V stored rows x ONE tile of T = 128*TM dense columns
+// ("tokens": SpMM columns of B, or SpConv output positions).  For an item the kernel
+// computes the dense contraction
 //
 //     acc[token][m] = sum_p  G[p][token] * W[p][m]          p over the block's non-zero columns
 //
-// on the 5th-generation tensor cores.  Mapping: tokens are the UMMA M dimension (128 TMEM
-// lanes, always the full-rate shape), the V rows of the block are the UMMA N dimension
-// (32/64/128 all legal), K = 16 per instruction.  Both operands are MN-major in shared
-// memory: W[p][0..V) is a contiguous slice of the value panels and G[p][..] is row
-// indices[p] of the dense operand, gathered.
+// on the 5th-generation tensor cores.  Tokens are the UMMA M dimension (128 TMEM lanes, the
+// full-rate shape), the V rows of the block the UMMA N dimension (32/64/128 all legal),
+// K = 16 per instruction.  Both operands are MN-major in shared memory: W[p][0..V) is a
+// contiguous slice of the value panels, G[p][..] is row indices[p] of the dense operand,
+// gathered from L2.
 //
-//   warps 0-3  producers: 16-byte cp.async gathers into 128-byte-swizzled stages, then the
-//              epilogue (TMEM -> registers -> fp16 -> global, inverse row permutation fused)
-//   warp  4    allocates TMEM, issues tcgen05.mma (one elected lane), frees stages with
-//              tcgen05.commit, frees TMEM
+// One CTA per SM loops over items (item = blockIdx.x + i*gridDim.x); their extents are read
+// once into a shared-memory table.  Warp roles:
+//   warps 0-7        epilogue: TMEM -> registers -> fp16 -> global (inverse row permutation
+//                    fused); warp w reads TMEM lane quadrant w % 4, column half w / 4
+//   warp  8          allocates TMEM, issues tcgen05.mma (lane 0), releases stages and
+//                    accumulators with tcgen05.commit
+//   warps 9..9+PW-1  producers: 16-byte cp.async gathers into 128-byte-swizzled stages.
+//                    A warp runs LAG stages ahead of its own copies (cp.async groups) and
+//                    publishes a stage with ONE mbarrier arrival per warp; the ring has more
+//                    stages than LAG+1 so the MMA warp is not in lock-step with the producers.
+//                    Row ids are prefetched 3 stages ahead in registers.
+//                    The measured L2->SM gather rate on B200 grows with the number of
+//                    issuing warps (4 warps/SM: 5 TB/s, 16 warps/SM: 16 TB/s), hence many
+//                    producer warps.
+// The accumulator is double buffered in TMEM so the epilogue of item i overlaps the main
+// loop of item i+1, and the stage ring runs across item boundaries without draining.
 //
-// Stage hand-over uses mbarriers; every wait is bounded (sm100_ptx.cuh) so a logic error
-// cannot hang the GPU: the kernel records a code in the status word, drains and exits.
+// Every mbarrier wait is bounded (sm100_ptx.cuh): on a timeout the kernel records a code in
+// the status word, raises a CTA-wide abort flag, drains and exits; it cannot hang the GPU.
 //
 // Replaces SpmmBlockwiseKernel::mainLoop / epilogue (block_sparse/spmm/blockwise_kernel.h:99-294,
 // block_sparse/common/epilogue.h:6-135) and SpconvBlockwiseKernel::mainLoop
@@ -31,9 +45,7 @@
 
 namespace shflbw {
 
-constexpr int kPanelKS = 64;            // non-zero columns per pipeline stage
-constexpr int kPanelThreads = 160;      // 4 producer/epilogue warps + 1 MMA warp
-constexpr long long kWaitLimitCycles = 400000000LL;  // ~0.2 s at 2 GHz
+constexpr long long kWaitLimitCycles = 400000000LL;   // ~0.2 s at 2 GHz
 
 struct PanelParams {
     // sparse operand (kernel image)
@@ -43,6 +55,9 @@ struct PanelParams {
     const int* perm;         // [M] or nullptr
     int* status_word;
     float alpha, beta;
+    int num_items, tiles_n;  // work items = row blocks x token tiles; item -> (item / tiles_n, item % tiles_n)
+    unsigned long long* trace;  // tuning builds only: per-role timestamps of CTA 0
+    int ablate;              // tuning builds only (-DSHFLBW_ABLATE): 1 no MMA, 2 no gather, 4 no value copies, 8 no stores
     // SpMM
     const __half* B;         // [K][N]
     const __half* C;         // [M][N] or nullptr
@@ -54,24 +69,30 @@ struct PanelParams {
     int Bn, Bp, Hin, Win, Cin, F, R, S, stride, Ho, Wo;
 };
 
-template <int V, int TM, int STAGES>
+template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
 struct PanelCfg {
-    static constexpr int KS = kPanelKS;
+    static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
+    static constexpr int THREADS = (9 + PW) * 32;
     static constexpr int G_ACC = KS * 256;                 // gathered tile of one accumulator: [KS][128] fp16
     static constexpr int G_BYTES = TM * G_ACC;
     static constexpr int W_BYTES = KS * V * 2;
     static constexpr int STAGE_BYTES = G_BYTES + W_BYTES;
     static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int OUT_BYTES = V * T * 2;            // SpMM epilogue staging [V][T] fp16
-    static constexpr int DATA_BYTES = PIPE_BYTES > OUT_BYTES ? PIPE_BYTES : OUT_BYTES;
-    static constexpr int BAR_BYTES = 256;                  // mbarriers + tmem slot + abort flag
-    static constexpr int ROWID_BYTES = V * 4;
-    static constexpr int SMEM_BYTES = DATA_BYTES + BAR_BYTES + ROWID_BYTES + 1024;  // + align slack
-    static constexpr uint32_t TMEM_COLS = TM * V < 32 ? 32 : TM * V;
+    static constexpr int OUT_BYTES = 0;                     // the epilogue stores straight from registers
+    static constexpr int BAR_BYTES = (STAGES * 2 + 8) * 8;   // mbarriers + tmem slot + abort flag
+    static constexpr int TAB_BYTES = 512 * 8;               // per-CTA item table (kPanelMaxItemsPerCta entries)
+    static constexpr int IDX_RING = 8;                      // stages of row ids kept in shared memory
+    static constexpr int IDX_BYTES = IDX_RING * KS * 4;
+    static constexpr int SMEM_BYTES = PIPE_BYTES + OUT_BYTES + BAR_BYTES + TAB_BYTES + IDX_BYTES + 1024;  // + align slack
+    static constexpr uint32_t ACC_COLS = TM * V;            // fp32 columns of one accumulator set
+    static constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // double buffered
     static_assert(V == 32 || V == 64 || V == 128, "row-block height");
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte swizzle-atom alignment");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
+    static_assert(KS % 16 == 0 && KS % PW == 0 && (KS / PW) % (32 / (T / 8)) == 0, "rows per producer warp");
+    static_assert(LAG_ >= 1 && LAG_ < STAGES && LAG_ + 2 <= IDX_RING, "a warp may run at most STAGES-1 stages ahead of its own copies");
+    static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
 // Shared-memory tile layouts (MN-major operands; r = K row inside the stage, c = 16-byte
@@ -88,40 +109,65 @@ __device__ __forceinline__ uint32_t tile128_off(int r, int c) {
 __device__ __forceinline__ uint32_t tile64_off(int r, int c) { return (uint32_t)(r * 128 + ((c ^ (r & 7)) << 4)); }
 __device__ __forceinline__ uint32_t tile32_off(int r, int c) { return (uint32_t)(r * 64 + ((c ^ ((r >> 1) & 3)) << 4)); }
 
-template <int V, int TM, int STAGES, bool CONV>
-__global__ void __launch_bounds__(kPanelThreads)
+constexpr int kPanelMaxItemsPerCta = 512;  // capacity of the per-CTA item table
+
+template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
+__global__ void __launch_bounds__((9 + PW) * 32, 1)
 panel_umma_kernel(const PanelParams p) {
-    using Cfg = PanelCfg<V, TM, STAGES>;
+    using Cfg = PanelCfg<V, TM, KS_, STAGES, LAG_, PW, CONV>;
     constexpr int KS = Cfg::KS, T = Cfg::T;
-    constexpr int LAG = STAGES > 2 ? 2 : 1;  // cp.async groups in flight per thread before publishing
+    constexpr int LAG = LAG_;  // stages a producer warp runs ahead of its own landed copies
+    constexpr int PFD = LAG + 1;  // row-id prefetch distance in stages: ids land with the group published one iteration earlier
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: swizzle atoms are addressed by absolute shared-memory address bits.
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    uint64_t* full_bar = (uint64_t*)(smem + Cfg::DATA_BYTES);
-    uint64_t* empty_bar = full_bar + STAGES;
-    uint64_t* accum_bar = empty_bar + STAGES;
-    uint32_t* tmem_slot = (uint32_t*)(accum_bar + 1);
+    uint8_t* bar_area = smem + Cfg::PIPE_BYTES + Cfg::OUT_BYTES;
+    uint64_t* full_bar = (uint64_t*)bar_area;          // [STAGES] producers -> MMA
+    uint64_t* empty_bar = full_bar + STAGES;           // [STAGES] MMA -> producers
+    uint64_t* acc_full = empty_bar + STAGES;           // [2] MMA -> epilogue
+    uint64_t* acc_empty = acc_full + 2;                // [2] epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* cta_abort = (volatile int*)(tmem_slot + 1);
-    int* row_ids = (int*)(smem + Cfg::DATA_BYTES + Cfg::BAR_BYTES);
+    int2* item_tab = (int2*)(bar_area + Cfg::BAR_BYTES);  // [nloc] (first padded row, padded row count)
+    int* idx_ring = (int*)(bar_area + Cfg::BAR_BYTES + Cfg::TAB_BYTES);  // [IDX_RING][KS] row ids of upcoming stages
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int blk = blockIdx.y;
-    const int n0 = blockIdx.x * T;
-    const int row_begin = p.blk_ptr[blk];
-    const int rows_total = p.blk_ptr[blk + 1] - row_begin;  // multiple of 16
-    const int num_stages_k = (rows_total + KS - 1) / KS;
+#ifdef SHFLBW_ABLATE
+    const int ablate = p.ablate;
+    auto now = []() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; };
+    const bool tracing = p.trace != nullptr && blockIdx.x == 0;
+#define TRACE(role, n, k) do { if (tracing && (n) < 256 && !(ablate & 256)) p.trace[(role) * 1024 + (n) * 4 + (k)] = now(); } while (0)
+#define CTRACE(k) do { if (p.trace != nullptr) p.trace[4096 + blockIdx.x * 8 + (k)] = now(); } while (0)
+#else
+#define CTRACE(k) do { } while (0)
+    constexpr int ablate = 0;
+#define TRACE(role, n, k) do { } while (0)
+#endif
+    // This CTA's work items: blockIdx.x, blockIdx.x + gridDim.x, ...  (host guarantees nloc <= table size)
+    const int nloc = (p.num_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
+    if (tid == 0) CTRACE(0);
     if (tid == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            sm100::mbar_init(&full_bar[s], 128);  // every producer thread arrives once per fill
+            // One arrival per producer WARP.  Per-thread deferred arrivals
+            // (cp.async.mbarrier.arrive.noinc) were measured at ~3 clk of load/store-unit time
+            // per thread, i.e. more than the copies themselves.
+            sm100::mbar_init(&full_bar[s], PW);
             sm100::mbar_init(&empty_bar[s], 1);   // one tcgen05.commit per drain
         }
-        sm100::mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            sm100::mbar_init(&acc_full[b], 1);
+            sm100::mbar_init(&acc_empty[b], 8);   // one arrival per epilogue warp
+        }
         *cta_abort = 0;
         sm100::mbar_init_fence();
     }
-    if (tid < V) row_ids[tid] = p.perm ? p.perm[blk * V + tid] : blk * V + tid;
-    if (warp == 4) {
+    for (int li = tid; li < nloc; li += blockDim.x) {
+        const int blk = ((int)blockIdx.x + li * (int)gridDim.x) / p.tiles_n;
+        const int b0 = __ldg(p.blk_ptr + blk);
+        item_tab[li] = make_int2(b0, __ldg(p.blk_ptr + blk + 1) - b0);
+    }
+    if (warp == 8) {
         sm100::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
         sm100::tmem_relinquish();
     }
@@ -130,60 +176,107 @@ panel_umma_kernel(const PanelParams p) {
     sm100::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t smem_base = sm100::smem_u32(smem);
+    if (tid == 0) TRACE(3, 0, 0);
+    if (tid == 0) CTRACE(1);
 
-    if (warp < 4) {
+    if (warp >= 9) {
         // ------------------------------------------------------------- producers ----
-        // Warp w owns rows [16w, 16w+16) of every stage = exactly K-step w of that stage.
+        const int pw = warp - 9;
+        constexpr int RPW = KS / PW;           // rows of a stage owned by this warp
         constexpr int CPR = T / 8;             // 16-byte chunks per gathered row
         constexpr int RPI = 32 / CPR;          // rows per warp instruction (TM=2: 1, TM=1: 2)
         const int chunk = lane % CPR;          // this lane's chunk of the token tile
         const int acc_id = chunk >> 4, c16 = chunk & 15;
-        const int tok0 = n0 + chunk * 8;       // first token of the chunk
-        const bool chunk_ok = tok0 < p.N;
+        const int ptid = pw * 32 + lane;
 
-        // SpConv: decode this lane's output position once.
-        int ho = 0, wo = 0, nn = 0;
-        if constexpr (CONV) {
-            const int pix = tok0 / p.Bp;
-            nn = tok0 - pix * p.Bp;
-            ho = pix / p.Wo;
-            wo = pix - ho * p.Wo;
-        }
-        const __half* lane_src0 = CONV ? p.Xs : p.B + tok0;
-
-        auto load_idx = [&](int it) -> int {  // lane j < 16 holds the column id of row 16w+j
-            const int r = it * KS + warp * 16 + (lane & 15);
-            return (it < num_stages_k && r < rows_total) ? __ldg(p.blk_idx + row_begin + r) : 0;
+        // A cursor walks the flattened (item, stage) sequence of this CTA using the item table.
+        struct Cursor { int li, kt, num_k, row_begin, rows_total; };
+        auto enter = [&](Cursor& c) {           // position on the first stage of item c.li (skipping empty items)
+            c.kt = 0;
+            while (c.li < nloc) {
+                const int2 e = item_tab[c.li];
+                c.row_begin = e.x; c.rows_total = e.y; c.num_k = (e.y + KS - 1) / KS;
+                if (c.num_k > 0) return;
+                ++c.li;
+            }
+            c.num_k = 0; c.row_begin = 0; c.rows_total = 0;
         };
-        int idx_cur = load_idx(0);
+        auto advance = [&](Cursor& c) { if (++c.kt >= c.num_k) { ++c.li; enter(c); } };
+        // Row ids are prefetched PFD stages ahead with 4-byte cp.async into a shared-memory ring
+        // (slot = stage % IDX_RING; this warp owns entries [pw*RPW, pw*RPW + RPW) of a slot).  A
+        // register prefetch does not work here: rotating the registers forces a wait on the
+        // in-flight load every iteration, i.e. one full L2 latency per stage.
+        auto prefetch_idx = [&](const Cursor& c, int stage_no) {
+            if (lane < RPW) {
+                const int r = c.kt * KS + pw * RPW + lane;
+                const bool ok = c.li < nloc && r < c.rows_total;
+                sm100::cp_async_4(sm100::smem_u32(idx_ring + (stage_no % Cfg::IDX_RING) * KS + pw * RPW + lane),
+                                  ok ? p.blk_idx + c.row_begin + r : p.blk_idx, ok ? 4u : 0u);
+            }
+        };
 
-        for (int it = 0; it < num_stages_k; ++it) {
-            const int s = it % STAGES;
-            if (it >= STAGES)
-                sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
-                                         SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles);
-            const int idx_next = load_idx(it + 1);
-            const int rows_valid = min(KS, rows_total - it * KS);  // multiple of 16
+        Cursor cur{0, 0, 0, 0, 0}, pre{0, 0, 0, 0, 0};
+        enter(cur);
+        pre = cur;
+        for (int d = 0; d < PFD; ++d) { prefetch_idx(pre, d); advance(pre); }
+        sm100::cp_async_commit();
+        sm100::cp_async_wait<0>();
+        __syncwarp();
+
+        int it = 0;       // stage counter across items
+        int cur_li = -1;  // item the per-lane token decode below belongs to
+        int tok0 = 0, ho = 0, wo = 0, nn = 0;
+        bool chunk_ok = false;
+        const __half* lane_src0 = p.B;
+
+        while (cur.li < nloc) {
+            if (cur.li != cur_li) {  // new item: decode this lane's tokens
+                cur_li = cur.li;
+                const int item = (int)blockIdx.x + cur.li * (int)gridDim.x;
+                tok0 = (item % p.tiles_n) * T + chunk * 8;
+                chunk_ok = tok0 < p.N;
+                if constexpr (CONV) {
+                    const int pix = tok0 / p.Bp;
+                    nn = tok0 - pix * p.Bp;
+                    ho = pix / p.Wo;
+                    wo = pix - ho * p.Wo;
+                } else {
+                    lane_src0 = p.B + tok0;
+                }
+            }
+            const int s = it % STAGES, s_idx = it % Cfg::IDX_RING;
+            if (it >= STAGES) {  // one lane polls; the warp follows through __syncwarp
+                if (lane == 0)
+                    sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
+                                             SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles);
+                __syncwarp();
+            }
+            if (pw == 0 && lane == 0) TRACE(0, it, 0);
+            prefetch_idx(pre, it + PFD);   // joins this iteration's cp.async group
+            advance(pre);
+            const int idx0 = idx_ring[s_idx * KS + pw * RPW + (lane % RPW)];  // landed: its group was awaited last iteration
+            const int rows_valid = min(KS, cur.rows_total - cur.kt * KS);  // multiple of 16
             const uint32_t g_base = smem_base + s * Cfg::STAGE_BYTES;
             const uint32_t w_base = g_base + Cfg::G_BYTES;
 
-            if (warp * 16 < rows_valid) {
-                // Per-row decode for SpConv: lane j works out (c, r, s) of its row, shared by shuffle.
-                int k_or_coff = idx_cur, rs_pack = 0;
-                if constexpr (CONV) {
-                    const int c = idx_cur % p.Cin, rs = idx_cur / p.Cin;
-                    const int fs = rs % p.S, fr = rs / p.S;
-                    k_or_coff = c * p.Hin * p.Win;
-                    rs_pack = (fr << 8) | fs;
-                }
+            // Per-row decode for SpConv: lane j works out (c, r, s) of its row, shared by shuffle.
+            int k_or_coff = idx0, rs_pack = 0;
+            if constexpr (CONV) {
+                const int c = idx0 % p.Cin, rs = idx0 / p.Cin;
+                const int fs = rs % p.S, fr = rs / p.S;
+                k_or_coff = c * p.Hin * p.Win;
+                rs_pack = (fr << 8) | fs;
+            }
 #pragma unroll
-                for (int q = 0; q < 16 / RPI; ++q) {
-                    const int jrow = q * RPI + (RPI == 2 ? (lane >> 4) : 0);  // row within the K-step
-                    const int kk = __shfl_sync(0xffffffffu, k_or_coff, jrow);
-                    const int r = warp * 16 + jrow;
+            for (int q = 0; q < RPW / RPI; ++q) {
+                const int jrow = q * RPI + (RPI == 2 ? (lane >> 4) : 0);  // row within this warp's slice
+                const int kk = __shfl_sync(0xffffffffu, k_or_coff, jrow);
+                int rs = 0;
+                if constexpr (CONV) rs = __shfl_sync(0xffffffffu, rs_pack, jrow);
+                const int r = pw * RPW + jrow;
+                if (r < rows_valid && !(ablate & 2)) {
                     const uint32_t dst = g_base + acc_id * Cfg::G_ACC + tile128_off(r, c16);
                     if constexpr (CONV) {
-                        const int rs = __shfl_sync(0xffffffffu, rs_pack, jrow);
                         const int hi = ho * p.stride - (p.R >> 1) + (rs >> 8);
                         const int wi = wo * p.stride - (p.S >> 1) + (rs & 0xff);
                         const bool ok = chunk_ok && hi >= 0 && hi < p.Hin && wi >= 0 && wi < p.Win;
@@ -198,9 +291,9 @@ panel_umma_kernel(const PanelParams p) {
             // Value panel slice [rows_valid][V]: contiguous in global memory.
             {
                 constexpr int WCPR = V / 8;  // chunks per row
-                const __half* wsrc = p.blk_val + (size_t)(row_begin + it * KS) * V;
+                const __half* wsrc = p.blk_val + (size_t)(cur.row_begin + cur.kt * KS) * V;
                 const int nchunks = rows_valid * WCPR;
-                for (int q = tid; q < nchunks; q += 128) {
+                for (int q = ptid; q < nchunks && !(ablate & 4); q += PW * 32) {
                     const int r = q / WCPR, c = q % WCPR;
                     uint32_t off;
                     if constexpr (V == 32) off = tile32_off(r, c);
@@ -210,91 +303,162 @@ panel_umma_kernel(const PanelParams p) {
                 }
             }
             sm100::cp_async_commit();
-            idx_cur = idx_next;
+            if (pw == 0 && lane == 0) TRACE(0, it, 1);
+            // Publish the stage issued LAG iterations ago: this warp's copies for it have landed.
             if (it >= LAG) {
                 sm100::cp_async_wait<LAG>();
-                sm100::fence_proxy_async_smem();
-                sm100::mbar_arrive(&full_bar[(it - LAG) % STAGES]);
+                __syncwarp();
+                if (lane == 0) {
+                    sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+                    sm100::mbar_arrive(&full_bar[(it - LAG) % STAGES]);
+                }
             }
+            if (pw == 0 && lane == 0) TRACE(0, it, 2);
+            advance(cur);
+            ++it;
         }
         // Publish the last LAG stages.
         sm100::cp_async_wait<0>();
-        sm100::fence_proxy_async_smem();
-        for (int it = max(0, num_stages_k - LAG); it < num_stages_k; ++it)
-            sm100::mbar_arrive(&full_bar[it % STAGES]);
-
-        // -------------------------------------------------------------- epilogue ----
-        if (num_stages_k > 0) {
-            sm100::mbar_wait_bounded(accum_bar, 0, cta_abort, p.status_word, SHFLBW_DEVSTAT_TIMEOUT_ACCUM,
-                                     kWaitLimitCycles);
-            sm100::tc_fence_after_sync();
+        __syncwarp();
+        if (lane == 0) {
+            sm100::fence_proxy_async_smem();
+            for (int j = (it > LAG ? it - LAG : 0); j < it; ++j) sm100::mbar_arrive(&full_bar[j % STAGES]);
         }
-        const __half2 alpha2 = __float2half2_rn(p.alpha);
-
-        if constexpr (!CONV) {
-            // TMEM -> fp16 -> staging tile S[m][token] (reuses the drained pipeline stages).
-            __half* stage_out = (__half*)smem;
-#pragma unroll
-            for (int a = 0; a < TM; ++a) {
-#pragma unroll
-                for (int c0 = 0; c0 < V; c0 += 32) {
-                    uint32_t r[32];
-                    if (num_stages_k > 0) {
-                        sm100::tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + a * V + c0, r);
-                        sm100::tmem_ld_wait();
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = 0u;
-                    }
-                    const int t = a * 128 + warp * 32 + lane;
-#pragma unroll
-                    for (int j = 0; j < 32; ++j)
-                        stage_out[(c0 + j) * T + t] = __float2half_rn(__uint_as_float(r[j]));
-                }
+        if (pw == 0 && lane == 0) CTRACE(2);
+    } else if (warp == 8) {
+        // ------------------------------------------------------------ MMA warp ----
+        constexpr uint32_t idesc = sm100::make_idesc_f16_mnmajor(128, V);
+        // Descriptors are built once; per MMA only the 16-byte-granular start address field
+        // (low bits) advances.  A single thread issues every MMA, so scalar work between two
+        // tcgen05.mma instructions directly limits the tensor-pipe issue rate.
+        const uint64_t gdesc0 = sm100::make_smem_desc(smem_base, 1024, 2048, sm100::kSwizzle128B);
+        const uint64_t wdesc0 =
+            V == 32 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 512, 512, sm100::kSwizzle64B)
+          : V == 64 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 1024, sm100::kSwizzle128B)
+                    : sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 2048, sm100::kSwizzle128B);
+        constexpr uint32_t WSTEP = V == 32 ? 1024 : V == 64 ? 2048 : 4096;  // bytes per K-step of the value tile
+        int it = 0;
+        for (int li = 0; li < nloc; ++li) {
+            const int rows_total = item_tab[li].y;
+            const int num_k = (rows_total + KS - 1) / KS;
+            const int b = li & 1;
+            if (li >= 2) {
+                if (lane == 0)
+                    sm100::mbar_wait_bounded(&acc_empty[b], ((li >> 1) - 1) & 1, cta_abort, p.status_word,
+                                             SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 20);
+                __syncwarp();
             }
-            sm100::tc_fence_before_sync();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            // Coalesced write-out: one 16-byte chunk per thread, a full tile row per CPR lanes.
-            const __half2 beta2 = __float2half2_rn(p.beta);
-            const bool use_c = p.beta != 0.0f && p.C != nullptr;
-            for (int q = tid; q < V * CPR; q += 128) {
-                const int m = q / CPR, ch = q % CPR;
-                const int tok = n0 + ch * 8;
-                if (tok >= p.N) continue;
-                uint4 v = *(const uint4*)(stage_out + m * T + ch * 8);
-                __half2* h = (__half2*)&v;
-                const size_t g = (size_t)row_ids[m] * p.N + tok;
-                if (use_c) {
-                    uint4 cv = *(const uint4*)(p.C + g);
-                    const __half2* ch2 = (const __half2*)&cv;
+            const uint32_t acc_base = tmem_base + b * Cfg::ACC_COLS;
+            for (int kt = 0; kt < num_k; ++kt, ++it) {
+                const int s = it % STAGES;
+                if (lane == 0) {
+                    sm100::mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, cta_abort, p.status_word,
+                                             SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
+                    TRACE(1, it, 0);
+                    if (!(ablate & 16)) sm100::fence_proxy_async_smem();  // cp.async (generic proxy) data -> tensor-core (async proxy) reads
+                    sm100::tc_fence_after_sync();
+                    const int nk = (ablate & 1) ? 0 : min(KS, rows_total - kt * KS) / 16;
+                    const uint64_t gd = gdesc0 + (uint64_t)((uint32_t)(s * Cfg::STAGE_BYTES) >> 4);
+                    const uint64_t wd = wdesc0 + (uint64_t)((uint32_t)(s * Cfg::STAGE_BYTES) >> 4);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) h[e] = __hfma2(h[e], alpha2, __hmul2(ch2[e], beta2));
+                    for (int j = 0; j < KS / 16; ++j) {
+                        if (j < nk) {
+#pragma unroll
+                            for (int a = 0; a < TM; ++a)
+                                sm100::umma_f16_ss(acc_base + a * V, gd + (uint64_t)((a * Cfg::G_ACC + j * 4096) >> 4),
+                                                   wd + (uint64_t)((j * WSTEP) >> 4), idesc,
+                                                   j == 0 ? (uint32_t)(kt != 0) : 1u);
+                        }
+                    }
+                    if (ablate & 64) sm100::mbar_arrive(&empty_bar[s]);
+                    else sm100::umma_commit(&empty_bar[s]);  // stage may be refilled once these MMAs retire
+                    TRACE(1, it, 1);
+                }
+                __syncwarp();
+            }
+            if (lane == 0) {
+                if (num_k > 0 && !(ablate & 1)) sm100::umma_commit(&acc_full[b]);  // accumulator complete
+                else sm100::mbar_arrive(&acc_full[b]);                             // nothing to wait for
+            }
+            __syncwarp();
+        }
+        if (lane == 0) CTRACE(3);
+    } else {
+        // -------------------------------------------------------------- epilogue ----
+        // Eight warps: warp w reads TMEM lane quadrant w % 4 (tokens) and half w / 4 of the
+        // accumulator columns (the block's output rows / filters).
+        const int quad = warp & 3, half_id = warp >> 2;
+        constexpr int HALVES = Cfg::ACC_COLS >= 64 ? 2 : 1;   // a 32-column accumulator is not split
+        constexpr int COLS = Cfg::ACC_COLS / HALVES;          // fp32 columns handled by this warp
+        const bool reads = half_id < HALVES;
+        const __half alpha1 = __float2half_rn(p.alpha), beta1 = __float2half_rn(p.beta);
+        const __half2 alpha2 = __half2half2(alpha1);
+        for (int li = 0; li < nloc; ++li) {
+            const int item = (int)blockIdx.x + li * (int)gridDim.x;
+            const int blk = item / p.tiles_n;
+            const int n0 = (item % p.tiles_n) * T;
+            const bool has_k = item_tab[li].y > 0 && !(ablate & 1);
+            const int b = li & 1;
+            if (lane == 0)
+                sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
+                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles);
+            __syncwarp();
+            sm100::tc_fence_after_sync();
+            if (tid == 0) TRACE(2, li, 0);
+            // columns [col0, col0 + COLS) of the accumulator set: accumulator a = col / V, row m = col % V
+            const int col0 = half_id * COLS;
+            const uint32_t acc_base = tmem_base + ((uint32_t)(quad * 32) << 16) + b * Cfg::ACC_COLS + col0;
+#pragma unroll
+            for (int c0 = 0; c0 < COLS; c0 += 32) {
+                uint32_t r[32];
+                if (has_k && reads) {
+                    sm100::tmem_ld_32x32b_x32(acc_base + c0, r);
+                    sm100::tmem_ld_wait();
                 } else {
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) h[e] = __hmul2(h[e], alpha2);
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
                 }
-                *(uint4*)(p.D + g) = v;
-            }
-        } else {
-            // SpConv: thread = output position, registers = the block's V filters, which are
-            // contiguous in the pixel's F-vector in stored filter order.
+                if (c0 + 32 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
+                    sm100::tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
+                    if (tid == 0) TRACE(2, li, 1);
+                }
+                if (ablate & 512) continue;
+                const int a = (col0 + c0) / V, m0 = (col0 + c0) % V;   // 32 columns never straddle accumulators
+                const int tok = reads ? n0 + a * 128 + quad * 32 + lane : p.N;  // idle warps store nothing
+                if constexpr (!CONV) {
+                    // Thread = token, registers = 32 output rows of the block.  For a fixed row the
+                    // warp's 32 tokens are 64 contiguous bytes of D: one warp store per row straight
+                    // from registers; the inverse row permutation is the row index of that store.
+                    const bool ok = tok < p.N && !(ablate & 8);
+                    const bool use_c = p.beta != 0.0f && p.C != nullptr;
+                    const int* rowp = (p.perm && !(ablate & 1024)) ? p.perm + blk * V + m0 : nullptr;
 #pragma unroll
-            for (int a = 0; a < TM; ++a) {
-                const int tok = n0 + a * 128 + warp * 32 + lane;
-                const int pix = tok / p.Bp, img = tok - pix * p.Bp;
-                const bool ok = tok < p.N && img < p.Bn;
-                const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
-                __half* dst = p.out + ((size_t)(img * p.Ho + oh) * p.Wo + ow) * p.F + blk * V;
+                    for (int j0 = 0; j0 < 32; j0 += 8) {
+                        uint32_t off[8];
 #pragma unroll
-                for (int c0 = 0; c0 < V; c0 += 32) {
-                    uint32_t r[32];
-                    if (num_stages_k > 0) {
-                        sm100::tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(warp * 32) << 16) + a * V + c0, r);
-                        sm100::tmem_ld_wait();
-                    } else {
+                        for (int j = 0; j < 8; ++j) {  // warp-uniform address: one broadcast load per row
+                            const int row = rowp ? __ldg(rowp + j0 + j) : blk * V + m0 + j0 + j;
+                            off[j] = (uint32_t)row * (uint32_t)p.N + (uint32_t)tok;
+                        }
+                        if (ok) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) r[j] = 0u;
+                            for (int j = 0; j < 8; ++j) {
+                                __half h = __float2half_rn(__uint_as_float(r[j0 + j]));
+                                if (use_c) h = __hfma(h, alpha1, __hmul(p.C[off[j]], beta1));
+                                else h = __hmul(h, alpha1);
+                                p.D[off[j]] = h;
+                            }
+                        }
                     }
+                } else {
+                    // SpConv: thread = output position, registers = 32 consecutive filters of the
+                    // block, contiguous in the pixel's F-vector in stored filter order.
+                    const int pix = tok / p.Bp, img = tok - pix * p.Bp;
+                    const bool ok = tok < p.N && img < p.Bn && !(ablate & 8);
+                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                    __half* dst = p.out + ((size_t)(img * p.Ho + oh) * p.Wo + ow) * p.F + blk * V + m0;
                     if (ok) {
 #pragma unroll
                         for (int j = 0; j < 32; j += 8) {
@@ -305,52 +469,27 @@ panel_umma_kernel(const PanelParams p) {
                                 h[e] = __hmul2(__floats2half2_rn(__uint_as_float(r[j + 2 * e]),
                                                                  __uint_as_float(r[j + 2 * e + 1])),
                                                alpha2);
-                            *(uint4*)(dst + c0 + j) = v;
+                            *(uint4*)(dst + j) = v;
                         }
                     }
                 }
             }
-            sm100::tc_fence_before_sync();
+            if (tid == 0) TRACE(2, li, 3);
         }
-    } else {
-        // ------------------------------------------------------------ MMA warp ----
-        constexpr uint32_t idesc = sm100::make_idesc_f16_mnmajor(128, V);
-        for (int it = 0; it < num_stages_k; ++it) {
-            const int s = it % STAGES;
-            if (lane == 0) {
-                sm100::mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, cta_abort, p.status_word,
-                                         SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles);
-                sm100::tc_fence_after_sync();
-                const int nk = min(KS, rows_total - it * KS) / 16;
-                const uint32_t g_base = smem_base + s * Cfg::STAGE_BYTES;
-                const uint32_t w_base = g_base + Cfg::G_BYTES;
-                for (int j = 0; j < nk; ++j) {
-                    uint64_t wdesc;
-                    if constexpr (V == 32)
-                        wdesc = sm100::make_smem_desc(w_base + j * 1024, 512, 512, sm100::kSwizzle64B);
-                    else if constexpr (V == 64)
-                        wdesc = sm100::make_smem_desc(w_base + j * 2048, 1024, 1024, sm100::kSwizzle128B);
-                    else
-                        wdesc = sm100::make_smem_desc(w_base + j * 4096, 1024, 2048, sm100::kSwizzle128B);
-#pragma unroll
-                    for (int a = 0; a < TM; ++a) {
-                        const uint64_t gdesc = sm100::make_smem_desc(g_base + a * Cfg::G_ACC + j * 4096,
-                                                                     1024, 2048, sm100::kSwizzle128B);
-                        sm100::umma_f16_ss(tmem_base + a * V, gdesc, wdesc, idesc, (it | j) != 0 ? 1u : 0u);
-                    }
-                }
-                sm100::umma_commit(&empty_bar[s]);                          // stage may be refilled
-                if (it == num_stages_k - 1) sm100::umma_commit(accum_bar);  // accumulator complete
-            }
-            __syncwarp();
-        }
+        if (tid == 0) CTRACE(4);
     }
 
+    sm100::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 4) {
+    if (tid == 0) TRACE(3, 0, 1);
+    if (tid == 0) CTRACE(5);
+    if (warp == 8) {
         sm100::tc_fence_after_sync();
         sm100::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }
 }
+
+#undef TRACE
+#undef CTRACE
 
 }  // namespace shflbw

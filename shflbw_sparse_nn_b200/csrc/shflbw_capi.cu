@@ -39,32 +39,71 @@ int ensure_buffer(void** buf, size_t* have, size_t need) {
 
 // ---- kernel table -------------------------------------------------------------------
 using PanelKernel = void (*)(const shflbw::PanelParams);
-struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; };
+struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; };
 
-template <int V, int TM, int STAGES, bool CONV>
+template <int V, int TM, int KS, int STAGES, int LAG, int PW, bool CONV>
 PanelChoice choice() {
-    return {shflbw::panel_umma_kernel<V, TM, STAGES, CONV>, (size_t)shflbw::PanelCfg<V, TM, STAGES>::SMEM_BYTES,
-            shflbw::PanelCfg<V, TM, STAGES>::T, STAGES};
+    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, LAG, PW, CONV>;
+    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, LAG, PW, CONV>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
+            Cfg::THREADS};
 }
 
-// Tile selection.  tokens-per-CTA 256 halves the value-panel traffic per token and is the
-// default; 128 is used when the dense extent is too small to fill the GPU with 256.
-// SHFLBW_TILE=128|256 overrides (tuning aid).
+// Pipeline shape per (V, tile): non-zero columns per stage (KS), ring depth (as many stages
+// as fit in ~200 KB of shared memory) and LAG, the number of stages a producer warp keeps in
+// flight before it publishes the oldest.  variant 0 is the default; others are tuning aids
+// selected with SHFLBW_VARIANT.
+template <bool CONV, int PW>
+bool lookup(int V, int tile, int variant, PanelChoice* out) {
+    switch ((V * 1000 + tile) * 10 + variant) {
+        case 321280:  *out = choice<32, 1, 64, 8, 4, PW, CONV>(); return true;    // 20 KB stages
+        case 322560:  *out = choice<32, 2, 64, 5, 2, PW, CONV>(); return true;    // 36 KB
+        case 641280:  *out = choice<64, 1, 64, 8, 4, PW, CONV>(); return true;    // 24 KB
+        case 642560:  *out = choice<64, 2, 64, 5, 2, PW, CONV>(); return true;    // 40 KB
+        case 642561:  *out = choice<64, 2, 64, 5, 3, PW, CONV>(); return true;
+        case 642562:  *out = choice<64, 2, 32, 10, 5, PW, CONV>(); return true;   // 20 KB
+        case 642563:  *out = choice<64, 2, 32, 10, 6, PW, CONV>(); return true;
+        case 642564:  *out = choice<64, 2, 48, 6, 3, PW, CONV>(); return true;    // 30 KB
+        case 1281280: *out = choice<128, 1, 64, 6, 3, PW, CONV>(); return true;   // 32 KB
+        case 1282560: *out = choice<128, 2, 64, 4, 2, PW, CONV>(); return true;   // 48 KB
+        default: return false;
+    }
+}
+
+template <bool CONV>
+bool lookup_pw(int V, int tile, int pw, int variant, PanelChoice* out) {
+    return pw == 16 ? lookup<CONV, 16>(V, tile, variant, out) : lookup<CONV, 8>(V, tile, variant, out);
+}
+
+// Persistent launch: one CTA per SM, more only when a CTA's share would overflow its item table.
+unsigned persistent_grid(int num_items, int sms) {
+    int g = num_items < sms ? num_items : sms;
+    const int need = (num_items + shflbw::kPanelMaxItemsPerCta - 1) / shflbw::kPanelMaxItemsPerCta;
+    return (unsigned)(g > need ? g : need);
+}
+
+int sm_count() {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    return n;
+}
+
+// Tile selection.  A 256-token work item halves the value-panel traffic per token and is
+// the default; 128 is used when the dense extent is too small to give every SM a few items.
+// SHFLBW_TILE=128|256 and SHFLBW_PW=8|16 override (tuning aids).
 template <bool CONV>
 int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
-    int tile = 256;
-    const long long ctas256 = ((n_tokens + 255) / 256) * row_blocks;
-    if (ctas256 < 148 * 2) tile = 128;
+    int tile = 256, pw = 8;
+    const long long items256 = ((n_tokens + 255) / 256) * row_blocks;
+    if (items256 < 148 * 3) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
-    switch (V) {
-        case 32:  *out = tile == 256 ? choice<32, 2, 4, CONV>() : choice<32, 1, 4, CONV>(); break;
-        case 64:  *out = tile == 256 ? choice<64, 2, 4, CONV>() : choice<64, 1, 4, CONV>(); break;
-        case 128: *out = tile == 256 ? choice<128, 2, 4, CONV>() : choice<128, 1, 4, CONV>(); break;
-        default: return SHFLBW_ERR_UNSUPPORTED;
-    }
-    if (out->smem > 48 * 1024) {
-        CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
-    }
+    if (const char* e = getenv("SHFLBW_PW")) { int t = atoi(e); if (t == 8 || t == 16) pw = t; }
+    int variant = 0;
+    if (const char* e = getenv("SHFLBW_VARIANT")) variant = atoi(e);
+    if (!lookup_pw<CONV>(V, tile, pw, variant, out) && !lookup_pw<CONV>(V, tile, pw, variant = 0, out))
+        return SHFLBW_ERR_UNSUPPORTED;
+    out->variant = variant;
+    CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
     return SHFLBW_OK;
 }
 
@@ -151,6 +190,8 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
     if (N % 8) return SHFLBW_ERR_UNSUPPORTED;                   // 16-byte rows of fp16
     const uintptr_t al = (uintptr_t)B | (uintptr_t)D | (uintptr_t)C;
     if (al & 15) return SHFLBW_ERR_UNSUPPORTED;
+    if ((long long)m->nrow * N >= (1ll << 32) || (long long)m->ncol * N >= (1ll << 40))
+        return SHFLBW_ERR_UNSUPPORTED;                          // 32-bit element offsets into C / D
 
     out->M = m->nrow; out->N = N; out->K = m->ncol; out->V = m->brow;
     out->num_row_blocks = m->nrow / m->brow;
@@ -167,9 +208,13 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
         int rc = pick_panel<false>(m->brow, N, out->num_row_blocks, &ch);
         if (rc != SHFLBW_OK) return rc;
         out->kernel = SHFLBW_KERNEL_TCGEN05;
-        out->tokens_per_cta = ch.tokens; out->stages = ch.stages;
-        out->block_x = shflbw::kPanelThreads;
-        out->grid_x = (N + ch.tokens - 1) / ch.tokens; out->grid_y = out->num_row_blocks;
+        out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
+        out->tiles_n = (N + ch.tokens - 1) / ch.tokens;
+        out->num_items = out->tiles_n * out->num_row_blocks;
+        const int sms = sm_count();
+        if (sms <= 0) return SHFLBW_ERR_CUDA;
+        out->block_x = ch.threads;
+        out->grid_x = persistent_grid(out->num_items, sms); out->grid_y = 1;
         out->shared_mem_size = ch.smem;
     }
     out->init_success = 1;
@@ -184,23 +229,19 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
             st->blk_ptr, st->blk_idx, (const __half*)st->blk_val, st->perm, (const __half*)st->B,
             (const __half*)st->C, (__half*)st->D, st->M, st->N, st->V, st->alpha, st->beta);
     } else {
+        // The state is a POD and may have been copied: re-derive the function pointer from the
+        // recorded configuration (the shared-memory attribute was set at init).
         PanelChoice ch;
-        // Re-derive the function pointer from the recorded tile (the state is a POD and may
-        // have been copied); attribute setting already happened at init.
-        const int tm = st->tokens_per_cta / 128;
-        switch (st->V * 10 + tm) {
-            case 321: ch = choice<32, 1, 4, false>(); break;
-            case 322: ch = choice<32, 2, 4, false>(); break;
-            case 641: ch = choice<64, 1, 4, false>(); break;
-            case 642: ch = choice<64, 2, 4, false>(); break;
-            case 1281: ch = choice<128, 1, 4, false>(); break;
-            case 1282: ch = choice<128, 2, 4, false>(); break;
-            default: return SHFLBW_ERR_INVALID_ARG;
-        }
+        if (!lookup_pw<false>(st->V, st->tokens_per_cta, st->producer_warps, st->variant, &ch)) return SHFLBW_ERR_INVALID_ARG;
         shflbw::PanelParams p{};
         p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
         p.B = (const __half*)st->B; p.C = (const __half*)st->C; p.D = (__half*)st->D; p.N = st->N;
+        p.num_items = st->num_items; p.tiles_n = st->tiles_n;
+#ifdef SHFLBW_ABLATE
+        if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
+        if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
+#endif
         ch.fn<<<dim3(st->grid_x, st->grid_y), st->block_x, st->shared_mem_size, s>>>(p);
     }
     CK(cudaGetLastError());
@@ -266,8 +307,13 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     int rc = pick_panel<true>(f->brow, tokens, f->F / f->brow, &ch);
     if (rc != SHFLBW_OK) return rc;
     out->kernel = SHFLBW_KERNEL_TCGEN05;
-    out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->block_x = shflbw::kPanelThreads;
-    out->grid_x = (unsigned)((tokens + ch.tokens - 1) / ch.tokens); out->grid_y = f->F / f->brow;
+    out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
+    out->tiles_n = (int)((tokens + ch.tokens - 1) / ch.tokens);
+    out->num_items = out->tiles_n * (f->F / f->brow);
+    const int sms = sm_count();
+    if (sms <= 0) return SHFLBW_ERR_CUDA;
+    out->block_x = ch.threads;
+    out->grid_x = persistent_grid(out->num_items, sms); out->grid_y = 1;
     out->shared_mem_size = ch.smem;
     // Scratch owned by the filter handle, grown on demand.
     out->staged_in_bytes = (size_t)f->C * Hin * Win * Bp * 2;
@@ -297,16 +343,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
         return SHFLBW_OK;
     }
     PanelChoice ch;
-    const int tm = st->tokens_per_cta / 128;
-    switch (st->V * 10 + tm) {
-        case 321: ch = choice<32, 1, 4, true>(); break;
-        case 322: ch = choice<32, 2, 4, true>(); break;
-        case 641: ch = choice<64, 1, 4, true>(); break;
-        case 642: ch = choice<64, 2, 4, true>(); break;
-        case 1281: ch = choice<128, 1, 4, true>(); break;
-        case 1282: ch = choice<128, 2, 4, true>(); break;
-        default: return SHFLBW_ERR_INVALID_ARG;
-    }
+    if (!lookup_pw<true>(st->V, st->tokens_per_cta, st->producer_warps, st->variant, &ch)) return SHFLBW_ERR_INVALID_ARG;
     // 1. NHWC -> channel-major, batch-innermost staging.
     {
         const int P = st->Hin * st->Win;
@@ -325,6 +362,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     p.out = (__half*)(st->staged_out ? st->staged_out : st->ofmap);
     p.Bn = st->B; p.Bp = st->Bp; p.Hin = st->Hin; p.Win = st->Win; p.Cin = st->C; p.F = st->F;
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
+    p.num_items = st->num_items; p.tiles_n = st->tiles_n;
     ch.fn<<<dim3(st->grid_x, st->grid_y), st->block_x, st->shared_mem_size, s>>>(p);
     // 3. inverse filter permutation.
     if (st->staged_out) {

@@ -25,11 +25,12 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(smem_u32(bar))
                  : "memory");
 }
+// Non-blocking phase test.
 __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(smem_u32(bar)), "r"(parity)
@@ -38,25 +39,29 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 }
 
 // Bounded wait.  Polls until the phase with the given parity completes, the CTA-wide
-// abort flag is raised, or `limit_cycles` SM clocks pass.  On timeout it raises the abort
-// flag and records `code` in the global status word; the caller carries on (results are
-// then garbage, but every later wait returns at once and the kernel drains and exits).
+// abort flag is raised, or `limit_cycles` SM clocks pass.  Between polls the thread sleeps
+// `backoff_ns` so that waiting warps do not take issue slots from the warps doing work (a
+// tight poll loop in ~20 waiting warps slowed the working warps several-fold).  On timeout
+// it raises the abort flag and records `code` in the global status word; the caller carries
+// on (results are then garbage, but every later wait returns at once and the kernel drains
+// and exits).
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* cta_abort, int* status_word,
-                                                  int code, long long limit_cycles) {
+                                                  int code, long long limit_cycles,
+                                                  uint32_t backoff_ns = 40) {
     if (mbar_test(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
+        if (backoff_ns) __nanosleep(backoff_ns);
         if (mbar_test(bar, parity)) return true;
-        if (*cta_abort) return false;
-        if ((++spins & 0x3f) == 0) {
+        if ((++spins & 0xf) == 0) {
+            if (*cta_abort) return false;
             if (clock64() - t0 > limit_cycles) {
                 *cta_abort = 1;
                 atomicCAS(status_word, 0, code);
                 return false;
             }
-            __nanosleep(64);
         }
     }
 }
@@ -67,10 +72,21 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes)
                  : "memory");
 }
+// 4-byte global->shared copy (used to prefetch row ids); src_bytes = 0 stores zero.
+__device__ __forceinline__ void cp_async_4(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst_smem), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+// Deferred arrival: the mbarrier receives one arrival (already counted in its expected
+// count, hence .noinc) once all cp.async copies this thread has issued so far have landed.
+// The issuing thread does not wait.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Generic-proxy writes (cp.async, st.shared) -> visible to the async proxy (tcgen05.mma reads).
 __device__ __forceinline__ void fence_proxy_async_smem() {
