@@ -185,9 +185,31 @@ panel_umma_kernel(const PanelParams p) {
         constexpr int RPW = KS / PW;           // rows of a stage owned by this warp
         constexpr int CPR = T / 8;             // 16-byte chunks per gathered row
         constexpr int RPI = 32 / CPR;          // rows per warp instruction (TM=2: 1, TM=1: 2)
+        constexpr int NQ = RPW / RPI;          // gather copies per lane per stage
+        constexpr int WCPR = V / 8;            // 16-byte chunks per value-panel row
+        constexpr int WQ = (KS * WCPR + PW * 32 - 1) / (PW * 32);  // value copies per thread per stage
         const int chunk = lane % CPR;          // this lane's chunk of the token tile
-        const int acc_id = chunk >> 4, c16 = chunk & 15;
+        const int sub = RPI == 2 ? (lane >> 4) : 0;
         const int ptid = pw * 32 + lane;
+        // Everything that does not change from stage to stage is computed once: the rows this
+        // lane copies and the swizzled shared-memory offsets of its chunks inside a stage.  The
+        // kernel is issue-bound on scalar work, so the per-copy path is kept to an address IMAD.
+        int grow[NQ];
+        uint32_t goff[NQ];
+#pragma unroll
+        for (int q = 0; q < NQ; ++q) {
+            grow[q] = pw * RPW + q * RPI + sub;
+            goff[q] = (uint32_t)((chunk >> 4) * Cfg::G_ACC) + tile128_off(grow[q], chunk & 15);
+        }
+        int wrow[WQ];
+        uint32_t woff[WQ];
+#pragma unroll
+        for (int u = 0; u < WQ; ++u) {
+            const int q = ptid + u * PW * 32;
+            const int r = q / WCPR, c = q % WCPR;
+            wrow[u] = q < KS * WCPR ? r : KS;  // KS = never valid
+            woff[u] = (uint32_t)Cfg::G_BYTES + (V == 32 ? tile32_off(r, c) : V == 64 ? tile64_off(r, c) : tile128_off(r, c));
+        }
 
         // A cursor walks the flattened (item, stage) sequence of this CTA using the item table.
         struct Cursor { int li, kt, num_k, row_begin, rows_total; };
@@ -207,7 +229,7 @@ panel_umma_kernel(const PanelParams p) {
         // register prefetch does not work here: rotating the registers forces a wait on the
         // in-flight load every iteration, i.e. one full L2 latency per stage.
         auto prefetch_idx = [&](const Cursor& c, int stage_no) {
-            if (lane < RPW) {
+            if (lane < RPW && !(ablate & 2048)) {
                 const int r = c.kt * KS + pw * RPW + lane;
                 const bool ok = c.li < nloc && r < c.rows_total;
                 sm100::cp_async_4(sm100::smem_u32(idx_ring + (stage_no % Cfg::IDX_RING) * KS + pw * RPW + lane),
@@ -218,104 +240,91 @@ panel_umma_kernel(const PanelParams p) {
         Cursor cur{0, 0, 0, 0, 0}, pre{0, 0, 0, 0, 0};
         enter(cur);
         pre = cur;
+#pragma unroll 1
         for (int d = 0; d < PFD; ++d) { prefetch_idx(pre, d); advance(pre); }
         sm100::cp_async_commit();
         sm100::cp_async_wait<0>();
         __syncwarp();
 
-        int it = 0;       // stage counter across items
-        int cur_li = -1;  // item the per-lane token decode below belongs to
-        int tok0 = 0, ho = 0, wo = 0, nn = 0;
-        bool chunk_ok = false;
-        const __half* lane_src0 = p.B;
-
-        while (cur.li < nloc) {
-            if (cur.li != cur_li) {  // new item: decode this lane's tokens
-                cur_li = cur.li;
-                const int item = (int)blockIdx.x + cur.li * (int)gridDim.x;
-                tok0 = (item % p.tiles_n) * T + chunk * 8;
-                chunk_ok = tok0 < p.N;
-                if constexpr (CONV) {
-                    const int pix = tok0 / p.Bp;
-                    nn = tok0 - pix * p.Bp;
-                    ho = pix / p.Wo;
-                    wo = pix - ho * p.Wo;
-                } else {
-                    lane_src0 = p.B + tok0;
-                }
-            }
-            const int s = it % STAGES, s_idx = it % Cfg::IDX_RING;
-            if (it >= STAGES) {  // one lane polls; the warp follows through __syncwarp
-                if (lane == 0)
-                    sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
-                                             SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles);
-                __syncwarp();
-            }
-            if (pw == 0 && lane == 0) TRACE(0, it, 0);
-            prefetch_idx(pre, it + PFD);   // joins this iteration's cp.async group
-            advance(pre);
-            const int idx0 = idx_ring[s_idx * KS + pw * RPW + (lane % RPW)];  // landed: its group was awaited last iteration
-            const int rows_valid = min(KS, cur.rows_total - cur.kt * KS);  // multiple of 16
-            const uint32_t g_base = smem_base + s * Cfg::STAGE_BYTES;
-            const uint32_t w_base = g_base + Cfg::G_BYTES;
-
-            // Per-row decode for SpConv: lane j works out (c, r, s) of its row, shared by shuffle.
-            int k_or_coff = idx0, rs_pack = 0;
+        int it = 0;  // stage counter across items
+        for (int li = cur.li; li < nloc; ++li) {
+            const int2 ent = item_tab[li];
+            const int num_k = (ent.y + KS - 1) / KS;
+            if (num_k == 0) continue;
+            // per-item decode of this lane's tokens
+            const int item = (int)blockIdx.x + li * (int)gridDim.x;
+            const int tok0 = (item % p.tiles_n) * T + chunk * 8;
+            const bool chunk_ok = tok0 < p.N;
+            const uint32_t nbytes = chunk_ok ? 16u : 0u;
+            int ho = 0, wo = 0, nn = 0;
             if constexpr (CONV) {
-                const int c = idx0 % p.Cin, rs = idx0 / p.Cin;
-                const int fs = rs % p.S, fr = rs / p.S;
-                k_or_coff = c * p.Hin * p.Win;
-                rs_pack = (fr << 8) | fs;
+                const int pix = tok0 / p.Bp;
+                nn = tok0 - pix * p.Bp;
+                ho = (pix / p.Wo) * p.stride - (p.R >> 1);
+                wo = (pix % p.Wo) * p.stride - (p.S >> 1);
             }
+            const __half* lane_src0 = chunk_ok ? p.B + tok0 : p.B;   // SpMM: column tok0 of row 0
+            const size_t row_pitch = chunk_ok ? (size_t)p.N : 0;      // out-of-range chunks read B[0] with size 0
+            const __half* wsrc = p.blk_val + (size_t)ent.x * V + (size_t)ptid * 8;
+
+            for (int kt = 0; kt < num_k; ++kt, ++it) {
+                const int s = it % STAGES, s_idx = it % Cfg::IDX_RING;
+                if (it >= STAGES) {  // one lane polls; the warp follows through __syncwarp
+                    if (lane == 0)
+                        sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
+                                                 SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles, 100);
+                    __syncwarp();
+                }
+                if (pw == 0 && lane == 0) TRACE(0, it, 0);
+                prefetch_idx(pre, it + PFD);   // joins this iteration's cp.async group
+                advance(pre);
+                const int rows_valid = min(KS, ent.y - kt * KS);  // multiple of 16
+                const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
+                const int* ids = idx_ring + s_idx * KS;  // landed: their group was awaited last iteration
+
+                if constexpr (!CONV) {
 #pragma unroll
-            for (int q = 0; q < RPW / RPI; ++q) {
-                const int jrow = q * RPI + (RPI == 2 ? (lane >> 4) : 0);  // row within this warp's slice
-                const int kk = __shfl_sync(0xffffffffu, k_or_coff, jrow);
-                int rs = 0;
-                if constexpr (CONV) rs = __shfl_sync(0xffffffffu, rs_pack, jrow);
-                const int r = pw * RPW + jrow;
-                if (r < rows_valid && !(ablate & 2)) {
-                    const uint32_t dst = g_base + acc_id * Cfg::G_ACC + tile128_off(r, c16);
-                    if constexpr (CONV) {
-                        const int hi = ho * p.stride - (p.R >> 1) + (rs >> 8);
-                        const int wi = wo * p.stride - (p.S >> 1) + (rs & 0xff);
-                        const bool ok = chunk_ok && hi >= 0 && hi < p.Hin && wi >= 0 && wi < p.Win;
-                        const __half* src = ok ? p.Xs + ((size_t)(kk + hi * p.Win + wi) * p.Bp + nn) : p.Xs;
-                        sm100::cp_async_16(dst, src, ok ? 16u : 0u);
-                    } else {
-                        const __half* src = chunk_ok ? lane_src0 + (size_t)kk * p.N : p.B;
-                        sm100::cp_async_16(dst, src, chunk_ok ? 16u : 0u);
+                    for (int q = 0; q < NQ; ++q) {
+                        if (grow[q] < rows_valid && !(ablate & 2))
+                            sm100::cp_async_16(st_base + goff[q], lane_src0 + (size_t)ids[grow[q]] * row_pitch, nbytes);
+                    }
+                } else {
+                    // lane j < RPW decodes (c, r, s) of row pw*RPW + j once; the others get it by shuffle
+                    const int k = ids[pw * RPW + (lane % RPW)];
+                    const int c = k % p.Cin, rs = k / p.Cin;
+                    const int coff = c * p.Hin * p.Win, rs_pack = ((rs / p.S) << 8) | (rs % p.S);
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) {
+                        const int src_lane = q * RPI + sub;
+                        const int kk = __shfl_sync(0xffffffffu, coff, src_lane);
+                        const int rsq = __shfl_sync(0xffffffffu, rs_pack, src_lane);
+                        if (grow[q] < rows_valid && !(ablate & 2)) {
+                            const int hi = ho + (rsq >> 8), wi = wo + (rsq & 0xff);
+                            const bool ok = chunk_ok && hi >= 0 && hi < p.Hin && wi >= 0 && wi < p.Win;
+                            const __half* src = ok ? p.Xs + ((size_t)(kk + hi * p.Win + wi) * p.Bp + nn) : p.Xs;
+                            sm100::cp_async_16(st_base + goff[q], src, ok ? 16u : 0u);
+                        }
                     }
                 }
-            }
-            // Value panel slice [rows_valid][V]: contiguous in global memory.
-            {
-                constexpr int WCPR = V / 8;  // chunks per row
-                const __half* wsrc = p.blk_val + (size_t)(cur.row_begin + cur.kt * KS) * V;
-                const int nchunks = rows_valid * WCPR;
-                for (int q = ptid; q < nchunks && !(ablate & 4); q += PW * 32) {
-                    const int r = q / WCPR, c = q % WCPR;
-                    uint32_t off;
-                    if constexpr (V == 32) off = tile32_off(r, c);
-                    else if constexpr (V == 64) off = tile64_off(r, c);
-                    else off = tile128_off(r, c);
-                    sm100::cp_async_16(w_base + off, wsrc + (size_t)q * 8, 16u);
+                // Value panel slice [rows_valid][V]: contiguous in global memory.
+#pragma unroll
+                for (int u = 0; u < WQ; ++u) {
+                    if (wrow[u] < rows_valid && !(ablate & 4))
+                        sm100::cp_async_16(st_base + woff[u], wsrc + (size_t)(kt * KS * V + u * PW * 32 * 8), 16u);
                 }
-            }
-            sm100::cp_async_commit();
-            if (pw == 0 && lane == 0) TRACE(0, it, 1);
-            // Publish the stage issued LAG iterations ago: this warp's copies for it have landed.
-            if (it >= LAG) {
-                sm100::cp_async_wait<LAG>();
-                __syncwarp();
-                if (lane == 0) {
-                    sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-                    sm100::mbar_arrive(&full_bar[(it - LAG) % STAGES]);
+                sm100::cp_async_commit();
+                if (pw == 0 && lane == 0) TRACE(0, it, 1);
+                // Publish the stage issued LAG iterations ago: this warp's copies for it have landed.
+                if (it >= LAG) {
+                    sm100::cp_async_wait<LAG>();
+                    __syncwarp();
+                    if (lane == 0) {
+                        sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
+                        sm100::mbar_arrive(&full_bar[(it - LAG) % STAGES]);
+                    }
                 }
+                if (pw == 0 && lane == 0) TRACE(0, it, 2);
             }
-            if (pw == 0 && lane == 0) TRACE(0, it, 2);
-            advance(cur);
-            ++it;
         }
         // Publish the last LAG stages.
         sm100::cp_async_wait<0>();
@@ -355,23 +364,42 @@ panel_umma_kernel(const PanelParams p) {
                     sm100::mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, cta_abort, p.status_word,
                                              SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
                     TRACE(1, it, 0);
+#ifdef SHFLBW_ABLATE
+                    const long long c0 = clock64();
+#endif
                     if (!(ablate & 16)) sm100::fence_proxy_async_smem();  // cp.async (generic proxy) data -> tensor-core (async proxy) reads
+#ifdef SHFLBW_ABLATE
+                    const long long c1 = clock64();
+#endif
                     sm100::tc_fence_after_sync();
+#ifdef SHFLBW_ABLATE
+                    const long long c1b = clock64();
+                    if (tracing && it < 256) p.trace[3 * 1024 + it * 4 + 0] = c1b - c1;
+#endif
                     const int nk = (ablate & 1) ? 0 : min(KS, rows_total - kt * KS) / 16;
                     const uint64_t gd = gdesc0 + (uint64_t)((uint32_t)(s * Cfg::STAGE_BYTES) >> 4);
                     const uint64_t wd = wdesc0 + (uint64_t)((uint32_t)(s * Cfg::STAGE_BYTES) >> 4);
+                    // compact loop (not unrolled): the three roles share a small instruction cache
+                    uint64_t gdj = gd, wdj = wd;
+                    uint32_t accum = (uint32_t)(kt != 0);
+#pragma unroll 1
+                    for (int j = 0; j < nk; ++j) {
 #pragma unroll
-                    for (int j = 0; j < KS / 16; ++j) {
-                        if (j < nk) {
-#pragma unroll
-                            for (int a = 0; a < TM; ++a)
-                                sm100::umma_f16_ss(acc_base + a * V, gd + (uint64_t)((a * Cfg::G_ACC + j * 4096) >> 4),
-                                                   wd + (uint64_t)((j * WSTEP) >> 4), idesc,
-                                                   j == 0 ? (uint32_t)(kt != 0) : 1u);
-                        }
+                        for (int a = 0; a < TM; ++a)
+                            sm100::umma_f16_ss(acc_base + a * V, gdj + (uint64_t)((a * Cfg::G_ACC) >> 4), wdj, idesc, accum);
+                        gdj += 4096 >> 4;
+                        wdj += WSTEP >> 4;
+                        accum = 1u;
                     }
+#ifdef SHFLBW_ABLATE
+                    const long long c2 = clock64();
+#endif
                     if (ablate & 64) sm100::mbar_arrive(&empty_bar[s]);
                     else sm100::umma_commit(&empty_bar[s]);  // stage may be refilled once these MMAs retire
+#ifdef SHFLBW_ABLATE
+                    const long long c3 = clock64();
+                    if (tracing && it < 256) { p.trace[3 * 1024 + it * 4 + 1] = c1 - c0; p.trace[3 * 1024 + it * 4 + 2] = c2 - c1; p.trace[3 * 1024 + it * 4 + 3] = c3 - c2; }
+#endif
                     TRACE(1, it, 1);
                 }
                 __syncwarp();
@@ -401,14 +429,14 @@ panel_umma_kernel(const PanelParams p) {
             const int b = li & 1;
             if (lane == 0)
                 sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
-                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles);
+                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 200);
             __syncwarp();
             sm100::tc_fence_after_sync();
             if (tid == 0) TRACE(2, li, 0);
             // columns [col0, col0 + COLS) of the accumulator set: accumulator a = col / V, row m = col % V
             const int col0 = half_id * COLS;
             const uint32_t acc_base = tmem_base + ((uint32_t)(quad * 32) << 16) + b * Cfg::ACC_COLS + col0;
-#pragma unroll
+#pragma unroll 1   // one copy of the 32-column body: the three roles share a small instruction cache
             for (int c0 = 0; c0 < COLS; c0 += 32) {
                 uint32_t r[32];
                 if (has_k && reads) {
@@ -433,23 +461,18 @@ panel_umma_kernel(const PanelParams p) {
                     // from registers; the inverse row permutation is the row index of that store.
                     const bool ok = tok < p.N && !(ablate & 8);
                     const bool use_c = p.beta != 0.0f && p.C != nullptr;
-                    const int* rowp = (p.perm && !(ablate & 1024)) ? p.perm + blk * V + m0 : nullptr;
+                    // lane j fetches the destination row of block row m0 + j (one coalesced load);
+                    // the store loop broadcasts it with a shuffle
+                    const int my_row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m0 + lane) : blk * V + m0 + lane;
+                    const uint32_t my_off = (uint32_t)my_row * (uint32_t)p.N;
 #pragma unroll
-                    for (int j0 = 0; j0 < 32; j0 += 8) {
-                        uint32_t off[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {  // warp-uniform address: one broadcast load per row
-                            const int row = rowp ? __ldg(rowp + j0 + j) : blk * V + m0 + j0 + j;
-                            off[j] = (uint32_t)row * (uint32_t)p.N + (uint32_t)tok;
-                        }
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t off = __shfl_sync(0xffffffffu, my_off, j) + (uint32_t)tok;
+                        __half h = __float2half_rn(__uint_as_float(r[j]));
                         if (ok) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j) {
-                                __half h = __float2half_rn(__uint_as_float(r[j0 + j]));
-                                if (use_c) h = __hfma(h, alpha1, __hmul(p.C[off[j]], beta1));
-                                else h = __hmul(h, alpha1);
-                                p.D[off[j]] = h;
-                            }
+                            if (use_c) h = __hfma(h, alpha1, __hmul(p.C[off], beta1));
+                            else h = __hmul(h, alpha1);
+                            p.D[off] = h;
                         }
                     }
                 } else {

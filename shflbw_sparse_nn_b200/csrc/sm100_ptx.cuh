@@ -44,8 +44,9 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // tight poll loop in ~20 waiting warps slowed the working warps several-fold).  On timeout
 // it raises the abort flag and records `code` in the global status word; the caller carries
 // on (results are then garbage, but every later wait returns at once and the kernel drains
-// and exits).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
+// and exits).  Not inlined: it is called from many places and the kernels are
+// sensitive to instruction-cache footprint.
+__device__ __noinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
                                                   volatile int* cta_abort, int* status_word,
                                                   int code, long long limit_cycles,
                                                   uint32_t backoff_ns = 40) {
