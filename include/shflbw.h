@@ -42,7 +42,8 @@ enum {
     SHFLBW_ERR_CUDA = 4,           /* a CUDA runtime call failed (see shflbw_last_cuda_error) */
     SHFLBW_ERR_NOT_ON_DEVICE = 5,  /* op init before shflbw_matrix_to_device             */
     SHFLBW_ERR_DEVICE_TIMEOUT = 6, /* a bounded in-kernel wait gave up (status word set) */
-    SHFLBW_ERR_IO = 7
+    SHFLBW_ERR_IO = 7,
+    SHFLBW_ERR_TOO_LARGE = 8       /* needs more than a fixed built-in capacity           */
 };
 
 /* How shflbw_matrix_create_random fills values. */
@@ -233,6 +234,33 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream);
 /* End-to-end conv with HOST NHWC buffers. */
 int shflbw_spconv_host(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
                        const void* ifmap_host, void* ofmap_host, float alpha);
+
+/* SpConv for callers that must not allocate.  No counterpart in the reference project.
+ *
+ * Some hosts call this library from a place where device allocation is off limits: the
+ * execute hook of an inference-runtime plugin, a serving loop whose memory is carved up
+ * front by a pool (a late cudaMalloc would synchronise the whole device and can fail when
+ * the pool owns the GPU), or code that is being recorded for later replay.  The regular
+ * shflbw_spconv_init grows scratch buffers with cudaMalloc; this entry point does not.  It
+ * runs the same three kernels (relayout, panel kernel, inverse filter permutation) with
+ * their scratch in a fixed array of SHFLBW_STATIC_SCRATCH_BYTES that is part of the
+ * library image; every GPU that loads the library holds that array until the process exits.
+ *
+ *  - `filter` must already be on the device (shflbw_matrix_to_device, done at set-up time).
+ *  - ifmap / ofmap are NHWC device pointers exactly as for shflbw_spconv_init; the launch is
+ *    asynchronous on `stream`.
+ *  - Needs 2*C*Hin*Win*roundup8(B) bytes, plus 2*B*Ho*Wo*F when the filter is permuted, each
+ *    rounded up to 256.  More than the capacity -> SHFLBW_ERR_TOO_LARGE, nothing is launched.
+ *  - The first call on each device looks up the array's device address; make that first
+ *    call during set-up, before any stream capture on that device.
+ *  - All calls on a device share the one array and it keeps the previous call's contents.
+ *    Nothing in it has to start at zero (every byte that is read is written first by the
+ *    same call), but two calls that overlap on the GPU -- different streams, or another
+ *    thread -- race on it.  Serialise them.
+ *  - It calls no cudaMalloc / cudaFree and no allocating library routine. */
+#define SHFLBW_STATIC_SCRATCH_BYTES (32u * 1024u * 1024u)
+int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
+                                      const void* ifmap_nhwc, void* ofmap_nhwc, float alpha, void* stream);
 
 /* Number of kernel launches one exec call issues (for launch accounting). */
 int shflbw_spmm_launches_per_exec(const shflbw_spmm_state_t* st);

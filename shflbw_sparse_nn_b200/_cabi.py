@@ -12,7 +12,8 @@ from .build import LIB_PATH
 
 OK = 0
 ERR_INVALID_ARG, ERR_BAD_FORMAT, ERR_UNSUPPORTED, ERR_CUDA = 1, 2, 3, 4
-ERR_NOT_ON_DEVICE, ERR_DEVICE_TIMEOUT, ERR_IO = 5, 6, 7
+ERR_NOT_ON_DEVICE, ERR_DEVICE_TIMEOUT, ERR_IO, ERR_TOO_LARGE = 5, 6, 7, 8
+STATIC_SCRATCH_BYTES = 32 * 1024 * 1024
 VALUES_INT9_LIBC, VALUES_UNIFORM = 0, 1
 KERNEL_AUTO, KERNEL_TCGEN05, KERNEL_SIMT = 0, 1, 2
 
@@ -100,6 +101,8 @@ _PROTOS = {
     "shflbw_spconv_exec": (C.c_int, [C.POINTER(SpconvState), C.c_void_p]),
     "shflbw_spconv_host": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_float]),
     "shflbw_spconv_launches_per_exec": (C.c_int, [C.POINTER(SpconvState)]),
+    "shflbw_spconv_exec_static_scratch": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                                    C.c_float, C.c_void_p]),
 }
 
 _lib = None
@@ -132,6 +135,6 @@ def check(status: int, where: str) -> None:
     if status != OK:
         l = lib()
         detail = l.shflbw_strerror(status).decode()
-        if status in (ERR_CUDA, ERR_DEVICE_TIMEOUT):
+        if status in (ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_TOO_LARGE):
             detail += "; " + l.shflbw_last_cuda_error().decode()
         raise ShflbwError(status, where, detail)

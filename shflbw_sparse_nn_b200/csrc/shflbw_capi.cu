@@ -114,6 +114,16 @@ int check_kernel_arg(int kernel) {
 
 }  // namespace
 
+// Scratch of shflbw_spconv_exec_static_scratch: part of the library image, present on every
+// GPU that loads the library.  In HOST code this name is only a handle for
+// cudaGetSymbolAddress -- it is not a device address and must never be handed to a kernel.
+static __device__ __align__(256) unsigned char g_static_scratch[SHFLBW_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};  // device address of the array, per device
+}  // namespace
+
 namespace shflbw {
 void drop_device_copy(shflbw_matrix& m) {
     void** bufs[] = {&m.d_meta, &m.d_val, &m.stage_in, &m.stage_c, &m.stage_out, &m.conv_in, &m.conv_out};
@@ -400,6 +410,73 @@ int shflbw_spconv_host(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     CK(cudaMemcpyAsync(ofmap_host, f->stage_out, bO, cudaMemcpyDeviceToHost, 0));
     CK(cudaStreamSynchronize(0));
     return SHFLBW_OK;
+}
+
+// SpConv without any allocation: scratch lives in g_static_scratch (see shflbw.h).
+int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, int Win, int stride,
+                                      const void* ifmap, void* ofmap, float alpha, void* stream) {
+    if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
+    if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
+    if (!f->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+    if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
+    if (((uintptr_t)ifmap | (uintptr_t)ofmap) & 15) return SHFLBW_ERR_UNSUPPORTED;
+    const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
+    const int Bp = (B + 7) / 8 * 8;
+    const long long tokens = (long long)Ho * Wo * Bp;
+    if ((long long)f->C * Hin * Win >= (1ll << 31) || tokens >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+
+    // Capacity check first: nothing is launched when the shape does not fit.
+    auto up256 = [](unsigned long long v) { return (v + 255ull) / 256ull * 256ull; };
+    const unsigned long long in_bytes = up256(2ull * f->C * Hin * Win * Bp);
+    const unsigned long long out_bytes = f->row_permute ? up256(2ull * B * Ho * Wo * f->F) : 0ull;
+    if (in_bytes + out_bytes > (unsigned long long)SHFLBW_STATIC_SCRATCH_BYTES) {
+        snprintf(g_cuda_err, sizeof g_cuda_err,
+                 "static scratch: this shape needs %llu bytes, the built-in array holds %u",
+                 in_bytes + out_bytes, (unsigned)SHFLBW_STATIC_SCRATCH_BYTES);
+        return SHFLBW_ERR_TOO_LARGE;
+    }
+
+    // Once per device, with that device current: the array's device address.
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return SHFLBW_ERR_UNSUPPORTED;
+    if (!g_static_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        CK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        if (!ptr) return SHFLBW_ERR_CUDA;
+        g_static_scratch_addr[dev] = ptr;
+    }
+    unsigned char* scratch = (unsigned char*)g_static_scratch_addr[dev];
+
+    // Same launch plan as shflbw_spconv_init, with the scratch pointers taken from the array.
+    shflbw_spconv_state_t st;
+    std::memset(&st, 0, sizeof st);
+    PanelChoice ch;
+    int rc = pick_panel<true>(f->brow, tokens, f->F / f->brow, &ch);
+    if (rc != SHFLBW_OK) return rc;
+    const int sms = sm_count();
+    if (sms <= 0) return SHFLBW_ERR_CUDA;
+    st.B = B; st.Hin = Hin; st.Win = Win; st.C = f->C; st.F = f->F; st.R = f->R; st.S = f->S;
+    st.stride = stride; st.Ho = Ho; st.Wo = Wo; st.V = f->brow; st.Bp = Bp;
+    st.kernel = SHFLBW_KERNEL_TCGEN05;
+    st.tokens_per_cta = ch.tokens; st.stages = ch.stages; st.producer_warps = ch.pw; st.variant = ch.variant;
+    st.tiles_n = (int)((tokens + ch.tokens - 1) / ch.tokens);
+    st.num_items = st.tiles_n * (f->F / f->brow);
+    st.block_x = ch.threads; st.grid_x = persistent_grid(st.num_items, sms); st.grid_y = 1;
+    st.shared_mem_size = ch.smem;
+    st.alpha = alpha; st.ifmap = ifmap; st.ofmap = ofmap;
+    st.staged_in = scratch; st.staged_in_bytes = (size_t)in_bytes;
+    if (f->row_permute) {
+        st.staged_out = scratch + in_bytes; st.staged_out_bytes = (size_t)out_bytes;
+        if ((size_t)f->F * 16 > 48 * 1024)
+            CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, f->F * 16));
+    }
+    st.blk_ptr = f->d_kptr; st.blk_idx = f->d_kidx; st.blk_val = f->d_val;
+    st.perm = f->d_perm; st.status_word = f->d_status;
+    st.init_success = 1;
+    return shflbw_spconv_exec(&st, stream);
 }
 
 }  // extern "C"

@@ -260,6 +260,7 @@ const char* shflbw_strerror(int status) {
         case SHFLBW_ERR_NOT_ON_DEVICE: return "matrix not uploaded (call shflbw_matrix_to_device)";
         case SHFLBW_ERR_DEVICE_TIMEOUT: return "a bounded in-kernel wait timed out";
         case SHFLBW_ERR_IO: return "file I/O error";
+        case SHFLBW_ERR_TOO_LARGE: return "request exceeds a fixed built-in capacity";
         default: return "unknown status";
     }
 }
