@@ -210,7 +210,7 @@ def run_ours(args):
     roofline = {"bound": bound, "achieved": round(achieved, 2), "peak": peak, "unit": runit,
                 "frac": round(achieved / peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
                 "peak_source": pk["source"], "algorithmic_bytes": bytes_alg, "algorithmic_flops": flops_nz,
-                "kernel": "panel_umma_kernel<64,2,4,false>", "kernel_us": round(t_kernel * 1e6, 3),
+                "kernel": "panel_umma_kernel<V=64,TM=2,KS=64,...,CONV=false>", "kernel_us": round(t_kernel * 1e6, 3),
                 "t_roof_us": round(max(t_tc, t_hbm) * 1e6, 3)}
 
     out = {
@@ -223,6 +223,16 @@ def run_ours(args):
         "dense_equivalent_tflops": round(world * flops_dense / (ms_step * 1e-3) / 1e12, 2),
         "roofline": roofline, "gpu_launches": args.steps * ops[0].launches_per_exec, "clocks": clocks,
     }
+
+    if args.quick:
+        if rank == 0 and world == 1:
+            out["spconv"] = bench_spconv(sb, torch, pk, steps=30, warmup=5)
+        if dist:
+            dist.barrier()
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps(out))
+        return
 
     # ---- end to end through the host-buffer C-ABI call (H2D + kernel + D2H inside the timing) ----
     e2e_steps = max(3, min(args.steps, 10))
@@ -346,7 +356,7 @@ def cpu_baseline_sample(m, threads: int, budget_s: float):
     nnz = m.nnzb * V_
     return {"value": round(2.0 * nnz * cols / wall / 1e12, 6), "unit": UNIT, "cores": threads,
             "kind": "reference" if use_ref else "port",
-            "sample": f"{cols} of {N_} dense columns ({per_thread} per thread), {wall:.2f} s wall",
+            "sample": f"{cols} dense columns of the {N_}-column workload ({per_thread} per thread), {wall:.2f} s wall",
             "seconds": round(wall, 3)}
 
 
@@ -387,6 +397,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--quick", action="store_true",
+                    help="profiling aid: timed SpMM loop plus a short SpConv loop only (no e2e, no reference kernels, no CPU baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

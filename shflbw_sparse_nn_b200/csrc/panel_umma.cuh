@@ -116,8 +116,6 @@ __global__ void __launch_bounds__((9 + PW) * 32, 1)
 panel_umma_kernel(const PanelParams p) {
     using Cfg = PanelCfg<V, TM, KS_, STAGES, LAG_, PW, CONV>;
     constexpr int KS = Cfg::KS, T = Cfg::T;
-    constexpr int LAG = LAG_;  // stages a producer warp runs ahead of its own landed copies
-    constexpr int PFD = LAG + 1;  // row-id prefetch distance in stages: ids land with the group published one iteration earlier
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: swizzle atoms are addressed by absolute shared-memory address bits.
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -152,7 +150,7 @@ panel_umma_kernel(const PanelParams p) {
             // One arrival per producer WARP.  Per-thread deferred arrivals
             // (cp.async.mbarrier.arrive.noinc) were measured at ~3 clk of load/store-unit time
             // per thread, i.e. more than the copies themselves.
-            sm100::mbar_init(&full_bar[s], PW);
+            sm100::mbar_init(&full_bar[s], PW / 2);
             sm100::mbar_init(&empty_bar[s], 1);   // one tcgen05.commit per drain
         }
         for (int b = 0; b < 2; ++b) {
@@ -181,31 +179,41 @@ panel_umma_kernel(const PanelParams p) {
 
     if (warp >= 9) {
         // ------------------------------------------------------------- producers ----
-        const int pw = warp - 9;
-        constexpr int RPW = KS / PW;           // rows of a stage owned by this warp
+        // The PW producer warps form GROUPS groups that take the CTA's stages in turn (group g
+        // fills stages g, g+GROUPS, ...).  While one group sits in its barrier round trip
+        // (wait for the free stage, wait for its copies, publish) the other one issues copies,
+        // so the load/store unit stays busy; with a single group the round trip (~400 clk)
+        // simply added to every stage.
+        constexpr int GROUPS = 2;
+        constexpr int GW = PW / GROUPS;        // warps that share one stage
+        constexpr int RPW = KS / GW;           // rows of a stage owned by this warp
         constexpr int CPR = T / 8;             // 16-byte chunks per gathered row
         constexpr int RPI = 32 / CPR;          // rows per warp instruction (TM=2: 1, TM=1: 2)
         constexpr int NQ = RPW / RPI;          // gather copies per lane per stage
         constexpr int WCPR = V / 8;            // 16-byte chunks per value-panel row
-        constexpr int WQ = (KS * WCPR + PW * 32 - 1) / (PW * 32);  // value copies per thread per stage
+        constexpr int WQ = (KS * WCPR + GW * 32 - 1) / (GW * 32);  // value copies per thread per stage
+        constexpr int XT = 8 / RPI;            // period of the swizzle term along q
+        static_assert(RPW % 8 == 0, "a producer warp owns whole 8-row swizzle groups");
+        const int grp = (warp - 9) / GW, pw = (warp - 9) % GW;
         const int chunk = lane % CPR;          // this lane's chunk of the token tile
         const int sub = RPI == 2 ? (lane >> 4) : 0;
         const int ptid = pw * 32 + lane;
-        // Everything that does not change from stage to stage is computed once: the rows this
-        // lane copies and the swizzled shared-memory offsets of its chunks inside a stage.  The
-        // kernel is issue-bound on scalar work, so the per-copy path is kept to an address IMAD.
-        int grow[NQ];
-        uint32_t goff[NQ];
+        // Everything that does not change from stage to stage is computed once.  Row q of this
+        // lane is r = pw*RPW + q*RPI + sub; its swizzled offset splits into a lane constant, a
+        // compile-time term in q and one of XT lane-dependent XOR terms.
+        const int rbase = pw * RPW + sub;
+        const uint32_t gbase = (uint32_t)((chunk >> 4) * Cfg::G_ACC + (pw * RPW / 8) * 2048 + (((chunk & 15) >> 3)) * 1024);
+        uint32_t gx[XT];
 #pragma unroll
-        for (int q = 0; q < NQ; ++q) {
-            grow[q] = pw * RPW + q * RPI + sub;
-            goff[q] = (uint32_t)((chunk >> 4) * Cfg::G_ACC) + tile128_off(grow[q], chunk & 15);
+        for (int j = 0; j < XT; ++j) {
+            const int r7 = (j * RPI + sub) & 7;
+            gx[j] = (uint32_t)(r7 * 128 + (((chunk & 7) ^ r7) << 4));
         }
         int wrow[WQ];
         uint32_t woff[WQ];
 #pragma unroll
         for (int u = 0; u < WQ; ++u) {
-            const int q = ptid + u * PW * 32;
+            const int q = ptid + u * GW * 32;
             const int r = q / WCPR, c = q % WCPR;
             wrow[u] = q < KS * WCPR ? r : KS;  // KS = never valid
             woff[u] = (uint32_t)Cfg::G_BYTES + (V == 32 ? tile32_off(r, c) : V == 64 ? tile64_off(r, c) : tile128_off(r, c));
@@ -224,10 +232,10 @@ panel_umma_kernel(const PanelParams p) {
             c.num_k = 0; c.row_begin = 0; c.rows_total = 0;
         };
         auto advance = [&](Cursor& c) { if (++c.kt >= c.num_k) { ++c.li; enter(c); } };
-        // Row ids are prefetched PFD stages ahead with 4-byte cp.async into a shared-memory ring
-        // (slot = stage % IDX_RING; this warp owns entries [pw*RPW, pw*RPW + RPW) of a slot).  A
-        // register prefetch does not work here: rotating the registers forces a wait on the
-        // in-flight load every iteration, i.e. one full L2 latency per stage.
+        // Row ids are prefetched with 4-byte cp.async into a shared-memory ring (slot = stage %
+        // IDX_RING; this warp owns entries [pw*RPW, pw*RPW + RPW) of its group's slots), two of
+        // the group's stages ahead, so they land with the copies awaited one iteration earlier.
+        // (A register prefetch would stall: rotating the registers waits for the load in flight.)
         auto prefetch_idx = [&](const Cursor& c, int stage_no) {
             if (lane < RPW && !(ablate & 2048)) {
                 const int r = c.kt * KS + pw * RPW + lane;
@@ -236,17 +244,23 @@ panel_umma_kernel(const PanelParams p) {
                                   ok ? p.blk_idx + c.row_begin + r : p.blk_idx, ok ? 4u : 0u);
             }
         };
+        static_assert(2 * GROUPS + GROUPS <= Cfg::IDX_RING, "row-id ring too small");
 
         Cursor cur{0, 0, 0, 0, 0}, pre{0, 0, 0, 0, 0};
         enter(cur);
         pre = cur;
+        for (int d = 0; d < grp; ++d) advance(pre);            // the group's first stage
 #pragma unroll 1
-        for (int d = 0; d < PFD; ++d) { prefetch_idx(pre, d); advance(pre); }
+        for (int d = 0; d < 2; ++d) {                          // ids of its first two stages
+            prefetch_idx(pre, grp + d * GROUPS);
+            for (int g = 0; g < GROUPS; ++g) advance(pre);
+        }
         sm100::cp_async_commit();
         sm100::cp_async_wait<0>();
         __syncwarp();
 
-        int it = 0;  // stage counter across items
+        int it = 0;        // stage counter across items (all groups count the same sequence)
+        int prev_s = -1;   // this group's previous stage, published one iteration later
         for (int li = cur.li; li < nloc; ++li) {
             const int2 ent = item_tab[li];
             const int num_k = (ent.y + KS - 1) / KS;
@@ -268,6 +282,7 @@ panel_umma_kernel(const PanelParams p) {
             const __half* wsrc = p.blk_val + (size_t)ent.x * V + (size_t)ptid * 8;
 
             for (int kt = 0; kt < num_k; ++kt, ++it) {
+                if ((it % GROUPS) != grp) continue;            // the other group's stage
                 const int s = it % STAGES, s_idx = it % Cfg::IDX_RING;
                 if (it >= STAGES) {  // one lane polls; the warp follows through __syncwarp
                     if (lane == 0)
@@ -276,8 +291,8 @@ panel_umma_kernel(const PanelParams p) {
                     __syncwarp();
                 }
                 if (pw == 0 && lane == 0) TRACE(0, it, 0);
-                prefetch_idx(pre, it + PFD);   // joins this iteration's cp.async group
-                advance(pre);
+                prefetch_idx(pre, it + 2 * GROUPS);            // joins this iteration's cp.async group
+                for (int g = 0; g < GROUPS; ++g) advance(pre);
                 const int rows_valid = min(KS, ent.y - kt * KS);  // multiple of 16
                 const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
                 const int* ids = idx_ring + s_idx * KS;  // landed: their group was awaited last iteration
@@ -285,8 +300,9 @@ panel_umma_kernel(const PanelParams p) {
                 if constexpr (!CONV) {
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) {
-                        if (grow[q] < rows_valid && !(ablate & 2))
-                            sm100::cp_async_16(st_base + goff[q], lane_src0 + (size_t)ids[grow[q]] * row_pitch, nbytes);
+                        if (rbase + q * RPI < rows_valid && !(ablate & 2))
+                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
+                                               lane_src0 + (size_t)ids[rbase + q * RPI] * row_pitch, nbytes);
                     }
                 } else {
                     // lane j < RPW decodes (c, r, s) of row pw*RPW + j once; the others get it by shuffle
@@ -298,11 +314,12 @@ panel_umma_kernel(const PanelParams p) {
                         const int src_lane = q * RPI + sub;
                         const int kk = __shfl_sync(0xffffffffu, coff, src_lane);
                         const int rsq = __shfl_sync(0xffffffffu, rs_pack, src_lane);
-                        if (grow[q] < rows_valid && !(ablate & 2)) {
+                        if (rbase + q * RPI < rows_valid && !(ablate & 2)) {
                             const int hi = ho + (rsq >> 8), wi = wo + (rsq & 0xff);
                             const bool ok = chunk_ok && hi >= 0 && hi < p.Hin && wi >= 0 && wi < p.Win;
                             const __half* src = ok ? p.Xs + ((size_t)(kk + hi * p.Win + wi) * p.Bp + nn) : p.Xs;
-                            sm100::cp_async_16(st_base + goff[q], src, ok ? 16u : 0u);
+                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT], src,
+                                               ok ? 16u : 0u);
                         }
                     }
                 }
@@ -310,29 +327,26 @@ panel_umma_kernel(const PanelParams p) {
 #pragma unroll
                 for (int u = 0; u < WQ; ++u) {
                     if (wrow[u] < rows_valid && !(ablate & 4))
-                        sm100::cp_async_16(st_base + woff[u], wsrc + (size_t)(kt * KS * V + u * PW * 32 * 8), 16u);
+                        sm100::cp_async_16(st_base + woff[u], wsrc + (size_t)(kt * KS * V + u * GW * 32 * 8), 16u);
                 }
                 sm100::cp_async_commit();
                 if (pw == 0 && lane == 0) TRACE(0, it, 1);
-                // Publish the stage issued LAG iterations ago: this warp's copies for it have landed.
-                if (it >= LAG) {
-                    sm100::cp_async_wait<LAG>();
+                // Publish the group's previous stage: this warp's copies for it have landed.
+                if (prev_s >= 0) {
+                    sm100::cp_async_wait<1>();
+                    sm100::fence_proxy_async_smem();   // every lane: its generic-proxy writes -> tensor-core reads
                     __syncwarp();
-                    if (lane == 0) {
-                        sm100::fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core
-                        sm100::mbar_arrive(&full_bar[(it - LAG) % STAGES]);
-                    }
+                    if (lane == 0) sm100::mbar_arrive(&full_bar[prev_s]);
                 }
+                prev_s = s;
                 if (pw == 0 && lane == 0) TRACE(0, it, 2);
             }
         }
-        // Publish the last LAG stages.
+        // Publish the group's last stage.
         sm100::cp_async_wait<0>();
+        sm100::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
-            sm100::fence_proxy_async_smem();
-            for (int j = (it > LAG ? it - LAG : 0); j < it; ++j) sm100::mbar_arrive(&full_bar[j % STAGES]);
-        }
+        if (lane == 0 && prev_s >= 0) sm100::mbar_arrive(&full_bar[prev_s]);
         if (pw == 0 && lane == 0) CTRACE(2);
     } else if (warp == 8) {
         // ------------------------------------------------------------ MMA warp ----
@@ -347,6 +361,7 @@ panel_umma_kernel(const PanelParams p) {
                     : sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 2048, sm100::kSwizzle128B);
         constexpr uint32_t WSTEP = V == 32 ? 1024 : V == 64 ? 2048 : 4096;  // bytes per K-step of the value tile
         int it = 0;
+        bool next_ready = false;  // lane 0: the coming stage's barrier was already seen complete
         for (int li = 0; li < nloc; ++li) {
             const int rows_total = item_tab[li].y;
             const int num_k = (rows_total + KS - 1) / KS;
@@ -361,8 +376,9 @@ panel_umma_kernel(const PanelParams p) {
             for (int kt = 0; kt < num_k; ++kt, ++it) {
                 const int s = it % STAGES;
                 if (lane == 0) {
-                    sm100::mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, cta_abort, p.status_word,
-                                             SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
+                    if (!next_ready)
+                        sm100::mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, cta_abort, p.status_word,
+                                                 SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
                     TRACE(1, it, 0);
 #ifdef SHFLBW_ABLATE
                     const long long c0 = clock64();
@@ -401,6 +417,8 @@ panel_umma_kernel(const PanelParams p) {
                     if (tracing && it < 256) { p.trace[3 * 1024 + it * 4 + 1] = c1 - c0; p.trace[3 * 1024 + it * 4 + 2] = c2 - c1; p.trace[3 * 1024 + it * 4 + 3] = c3 - c2; }
 #endif
                     TRACE(1, it, 1);
+                    // Test the next stage's barrier now: the round trip hides behind the MMAs just issued.
+                    next_ready = sm100::mbar_test(&full_bar[(it + 1) % STAGES], ((it + 1) / STAGES) & 1);
                 }
                 __syncwarp();
             }
@@ -436,38 +454,49 @@ panel_umma_kernel(const PanelParams p) {
             // columns [col0, col0 + COLS) of the accumulator set: accumulator a = col / V, row m = col % V
             const int col0 = half_id * COLS;
             const uint32_t acc_base = tmem_base + ((uint32_t)(quad * 32) << 16) + b * Cfg::ACC_COLS + col0;
-#pragma unroll 1   // one copy of the 32-column body: the three roles share a small instruction cache
-            for (int c0 = 0; c0 < COLS; c0 += 32) {
-                uint32_t r[32];
+            // per-item, per-thread constants
+            const int a0 = col0 / V;                       // this warp's columns lie in one accumulator
+            const int tok = reads ? n0 + a0 * 128 + quad * 32 + lane : p.N;   // idle warps store nothing
+            const int mbase = col0 % V;                    // first block row / filter of this warp
+            bool ok = tok < p.N && !(ablate & 8);
+            uint32_t my_off = 0;                           // SpMM: row offset of block row mbase + 32*g + lane
+            __half* dst = nullptr;                         // SpConv: this position's F-vector at the block's filters
+            if constexpr (CONV) {
+                const int pix = tok / p.Bp, img = tok - pix * p.Bp;
+                ok = ok && img < p.Bn;
+                const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                dst = p.out + ((size_t)(img * p.Ho + oh) * p.Wo + ow) * p.F + blk * V + mbase;
+            }
+            const bool use_c = p.beta != 0.0f && p.C != nullptr;
+#pragma unroll 1   // a short loop body: the three roles share a small instruction cache
+            for (int c0 = 0; c0 < COLS; c0 += 8) {
+                uint32_t r[8];
                 if (has_k && reads) {
-                    sm100::tmem_ld_32x32b_x32(acc_base + c0, r);
+                    sm100::tmem_ld_32x32b_x8(acc_base + c0, r);
                     sm100::tmem_ld_wait();
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                    for (int j = 0; j < 8; ++j) r[j] = 0u;
                 }
-                if (c0 + 32 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
+                if (c0 + 8 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
                     sm100::tc_fence_before_sync();
                     __syncwarp();
                     if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
                     if (tid == 0) TRACE(2, li, 1);
                 }
                 if (ablate & 512) continue;
-                const int a = (col0 + c0) / V, m0 = (col0 + c0) % V;   // 32 columns never straddle accumulators
-                const int tok = reads ? n0 + a * 128 + quad * 32 + lane : p.N;  // idle warps store nothing
                 if constexpr (!CONV) {
-                    // Thread = token, registers = 32 output rows of the block.  For a fixed row the
+                    // Thread = token, registers = 8 output rows of the block.  For a fixed row the
                     // warp's 32 tokens are 64 contiguous bytes of D: one warp store per row straight
                     // from registers; the inverse row permutation is the row index of that store.
-                    const bool ok = tok < p.N && !(ablate & 8);
-                    const bool use_c = p.beta != 0.0f && p.C != nullptr;
-                    // lane j fetches the destination row of block row m0 + j (one coalesced load);
-                    // the store loop broadcasts it with a shuffle
-                    const int my_row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m0 + lane) : blk * V + m0 + lane;
-                    const uint32_t my_off = (uint32_t)my_row * (uint32_t)p.N;
+                    if ((c0 & 31) == 0) {  // lane j fetches the destination row of block row mbase+c0+j
+                        const int m = mbase + c0 + lane;
+                        const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + (m < V ? m : V - 1)) : blk * V + m;
+                        my_off = (uint32_t)row * (uint32_t)p.N;
+                    }
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const uint32_t off = __shfl_sync(0xffffffffu, my_off, j) + (uint32_t)tok;
+                    for (int j = 0; j < 8; ++j) {
+                        const uint32_t off = __shfl_sync(0xffffffffu, my_off, (c0 & 31) + j) + (uint32_t)tok;
                         __half h = __float2half_rn(__uint_as_float(r[j]));
                         if (ok) {
                             if (use_c) h = __hfma(h, alpha1, __hmul(p.C[off], beta1));
@@ -476,24 +505,15 @@ panel_umma_kernel(const PanelParams p) {
                         }
                     }
                 } else {
-                    // SpConv: thread = output position, registers = 32 consecutive filters of the
+                    // SpConv: thread = output position, registers = 8 consecutive filters of the
                     // block, contiguous in the pixel's F-vector in stored filter order.
-                    const int pix = tok / p.Bp, img = tok - pix * p.Bp;
-                    const bool ok = tok < p.N && img < p.Bn && !(ablate & 8);
-                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
-                    __half* dst = p.out + ((size_t)(img * p.Ho + oh) * p.Wo + ow) * p.F + blk * V + m0;
                     if (ok) {
+                        uint4 v;
+                        __half2* h = (__half2*)&v;
 #pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 v;
-                            __half2* h = (__half2*)&v;
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                h[e] = __hmul2(__floats2half2_rn(__uint_as_float(r[j + 2 * e]),
-                                                                 __uint_as_float(r[j + 2 * e + 1])),
-                                               alpha2);
-                            *(uint4*)(dst + j) = v;
-                        }
+                        for (int e = 0; e < 4; ++e)
+                            h[e] = __hmul2(__floats2half2_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])), alpha2);
+                        *(uint4*)(dst + c0) = v;
                     }
                 }
             }

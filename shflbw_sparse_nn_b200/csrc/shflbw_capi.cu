@@ -60,9 +60,6 @@ bool lookup(int V, int tile, int variant, PanelChoice* out) {
         case 641280:  *out = choice<64, 1, 64, 8, 4, PW, CONV>(); return true;    // 24 KB
         case 642560:  *out = choice<64, 2, 64, 5, 2, PW, CONV>(); return true;    // 40 KB
         case 642561:  *out = choice<64, 2, 64, 5, 3, PW, CONV>(); return true;
-        case 642562:  *out = choice<64, 2, 32, 10, 5, PW, CONV>(); return true;   // 20 KB
-        case 642563:  *out = choice<64, 2, 32, 10, 6, PW, CONV>(); return true;
-        case 642564:  *out = choice<64, 2, 48, 6, 3, PW, CONV>(); return true;    // 30 KB
         case 1281280: *out = choice<128, 1, 64, 6, 3, PW, CONV>(); return true;   // 32 KB
         case 1282560: *out = choice<128, 2, 64, 4, 2, PW, CONV>(); return true;   // 48 KB
         default: return false;

@@ -38,19 +38,18 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Bounded wait.  Polls until the phase with the given parity completes, the CTA-wide
-// abort flag is raised, or `limit_cycles` SM clocks pass.  Between polls the thread sleeps
-// `backoff_ns` so that waiting warps do not take issue slots from the warps doing work (a
-// tight poll loop in ~20 waiting warps slowed the working warps several-fold).  On timeout
-// it raises the abort flag and records `code` in the global status word; the caller carries
-// on (results are then garbage, but every later wait returns at once and the kernel drains
-// and exits).  Not inlined: it is called from many places and the kernels are
-// sensitive to instruction-cache footprint.
-__device__ __noinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
-                                                  volatile int* cta_abort, int* status_word,
-                                                  int code, long long limit_cycles,
-                                                  uint32_t backoff_ns = 40) {
-    if (mbar_test(bar, parity)) return true;
+// Bounded wait.  Returns when the phase with the given parity completes, the CTA-wide abort
+// flag is raised, or `limit_cycles` SM clocks pass.  On timeout it raises the abort flag and
+// records `code` in the global status word; the caller carries on (results are then garbage,
+// but every later wait returns at once and the kernel drains and exits).
+//
+// The already-complete case is one inlined test; the polling loop lives in a function that is
+// NOT inlined, so the hot loops of the kernel stay short and straight (the kernels proved
+// sensitive to instruction fetch: a taken branch to a cold line cost ~150 clk).  Between
+// polls the thread sleeps `backoff_ns` so waiting warps leave the issue slots to the others.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
+                                            int* status_word, int code, long long limit_cycles,
+                                            uint32_t backoff_ns) {
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
@@ -65,6 +64,12 @@ __device__ __noinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity,
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
+                                                  int* status_word, int code, long long limit_cycles,
+                                                  uint32_t backoff_ns = 40) {
+    if (mbar_test(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, cta_abort, status_word, code, limit_cycles, backoff_ns);
 }
 
 // ------------------------------------------------------------------ cp.async ----
@@ -146,6 +151,13 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
           "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+// TMEM -> registers: the warp's 32 lanes x 8 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
