@@ -213,7 +213,7 @@ typedef struct shflbw_spconv_state {
     void* staged_out;        /* scratch: [B*Ho*Wo][F] in stored filter order, or NULL  */
     size_t staged_in_bytes, staged_out_bytes;
     const int* blk_ptr;
-    const int* blk_idx;
+    const int* blk_idx;      /* tensor-core path: ids decoded as c | r<<16 | s<<24 */
     const void* blk_val;
     const int* perm;
     int* status_word;

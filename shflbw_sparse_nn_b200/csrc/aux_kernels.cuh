@@ -7,55 +7,90 @@
 //     for bring-up and as an on-device cross-check of the tensor-core path.
 #pragma once
 
+#include <cstdint>
+
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
 namespace shflbw {
 
 // in[n][p][c] (NHWC, p = hi*Win + wi)  ->  Xs[c][p][Bp] with n < Bn copied and n >= Bn zero.
-// One block: 64 channels x 128 (pixel, image) slots; reads are contiguous along c, writes
-// contiguous along n.
+// One block: 64 channels x 128 (pixel, image) slots, images fastest.  Both global accesses
+// are 16 bytes per thread (8 channels in, 8 images out); the transpose happens in shared
+// memory, whose 8-slot groups are XOR-swizzled by the channel group so that neither the
+// 2-byte scatter nor the 16-byte read-back has bank conflicts.  Requires C % 8 == 0, Bp % 8 == 0.
 constexpr int kRelayoutC = 64, kRelayoutSlots = 128;
 __global__ void __launch_bounds__(256)
 relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, int Bn, int Bp, int P, int C) {
-    __shared__ __half tile[kRelayoutC][kRelayoutSlots + 2];
-    const int NT = Bp < 32 ? Bp : 32;        // images per tile (Bp is a multiple of 8)
+    __shared__ __align__(16) __half tile[kRelayoutC * kRelayoutSlots];
+    const int NT = Bp < 32 ? Bp : 32;        // images per tile (a multiple of 8)
     const int PT = kRelayoutSlots / NT;      // pixels per tile
     const int n_tiles = (Bp + NT - 1) / NT;
     const int p0 = (blockIdx.x / n_tiles) * PT, nb = (blockIdx.x % n_tiles) * NT;
     const int c0 = blockIdx.y * kRelayoutC;
-    // load: thread -> (slot, channel) with channel fastest
-    for (int e = threadIdx.x; e < kRelayoutC * kRelayoutSlots; e += 256) {
-        const int c = e % kRelayoutC, slot = e / kRelayoutC;
-        const int pl = slot / NT, nl = slot % NT;
+    // load: thread -> (slot, 8-channel chunk), chunk fastest: 8 lanes read 128 contiguous bytes
+    uint4 v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x + i * 256;
+        const int chunk = e & 7, slot = e >> 3;
+        const int pl = slot / NT, nl = slot - pl * NT;
         const int pp = p0 + pl, n = nb + nl;
-        __half v = __float2half(0.f);
-        if (pl < PT && pp < P && n < Bn && c0 + c < C) v = in[((size_t)n * P + pp) * C + c0 + c];
-        tile[c][slot] = v;
+        v[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (pl < PT && pp < P && n < Bn && c0 + chunk * 8 < C)
+            v[i] = __ldg((const uint4*)(in + ((size_t)n * P + pp) * C + c0 + chunk * 8));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x + i * 256;
+        const int chunk = e & 7, slot = e >> 3;
+        const __half* h = (const __half*)&v[i];
+        const int col = (((slot >> 3) ^ chunk) << 3) | (slot & 7);   // swizzled slot
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tile[(chunk * 8 + j) * kRelayoutSlots + col] = h[j];
     }
     __syncthreads();
-    // store: thread -> (channel, slot) with slot (image) fastest
-    for (int e = threadIdx.x; e < kRelayoutC * kRelayoutSlots; e += 256) {
-        const int slot = e % kRelayoutSlots, c = e / kRelayoutSlots;
-        const int pl = slot / NT, nl = slot % NT;
+    // store: thread -> (channel, 8-slot group), group fastest: 8 consecutive images of one pixel
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int e = threadIdx.x + i * 256;
+        const int g = e & 15, c = e >> 4;
+        const int slot = g * 8;
+        const int pl = slot / NT, nl = slot - pl * NT;
         const int pp = p0 + pl, n = nb + nl;
-        if (pl < PT && pp < P && n < Bp && c0 + c < C) Xs[((size_t)(c0 + c) * P + pp) * Bp + n] = tile[c][slot];
+        if (pl < PT && pp < P && n < Bp && c0 + c < C)
+            *(uint4*)(Xs + ((size_t)(c0 + c) * P + pp) * Bp + n) =
+                *(const uint4*)(tile + c * kRelayoutSlots + ((g ^ (c >> 3)) << 3));
     }
 }
 
-// out[q][perm[f]] = staged[q][f] for every output position q; one warp per position, the
-// F-vector is permuted in shared memory so both global accesses are contiguous.
+// out[q][perm[f]] = staged[q][f] for every output position q; one warp per position.  The
+// permutation sits in shared memory (read once per block); each lane moves 8 filters at a
+// time with 16-byte global accesses and scatters them into the warp's F-vector in shared
+// memory with 2-byte stores.  Dynamic shared memory: F*4 bytes (perm) + 8*F*2 bytes.  F % 8 == 0.
 __global__ void __launch_bounds__(256)
 unpermute_filters(const __half* __restrict__ staged, __half* __restrict__ out, const int* __restrict__ perm,
                   int num_pos, int F) {
-    extern __shared__ __half vec[];  // [8 warps][F]
+    extern __shared__ __align__(16) uint8_t unperm_smem[];
+    int* sperm = (int*)unperm_smem;                          // [F]
+    __half* vec = (__half*)(unperm_smem + (size_t)F * 4);     // [8 warps][F]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int f = threadIdx.x; f < F; f += 256) sperm[f] = __ldg(perm + f);
+    __syncthreads();
     __half* mine = vec + (size_t)warp * F;
     for (int q = blockIdx.x * 8 + warp; q < num_pos; q += gridDim.x * 8) {
         const __half* src = staged + (size_t)q * F;
-        for (int f = lane; f < F; f += 32) mine[perm[f]] = src[f];
+#pragma unroll 4
+        for (int f8 = lane * 8; f8 < F; f8 += 256) {
+            const uint4 v = *(const uint4*)(src + f8);
+            const int4 pa = *(const int4*)(sperm + f8), pb = *(const int4*)(sperm + f8 + 4);
+            const __half* h = (const __half*)&v;
+            mine[pa.x] = h[0]; mine[pa.y] = h[1]; mine[pa.z] = h[2]; mine[pa.w] = h[3];
+            mine[pb.x] = h[4]; mine[pb.y] = h[5]; mine[pb.z] = h[6]; mine[pb.w] = h[7];
+        }
         __syncwarp();
         __half* dst = out + (size_t)q * F;
+#pragma unroll 4
         for (int f8 = lane * 8; f8 < F; f8 += 256) *(uint4*)(dst + f8) = *(const uint4*)(mine + f8);
         __syncwarp();
     }

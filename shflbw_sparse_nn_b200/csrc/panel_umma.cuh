@@ -270,12 +270,19 @@ panel_umma_kernel(const PanelParams p) {
             const int tok0 = (item % p.tiles_n) * T + chunk * 8;
             const bool chunk_ok = tok0 < p.N;
             const uint32_t nbytes = chunk_ok ? 16u : 0u;
-            int ho = 0, wo = 0, nn = 0;
+            // SpConv: this lane's 8 tokens are 8 images of one output pixel.  Which filter taps
+            // (r, s) fall inside the input is a per-item property of the lane: two bit masks.
+            int base_off = 0;                  // staged-input offset of tap (0, 0), may be negative
+            uint32_t hmask = 0, wmask = 0;     // bit r / bit s: input row / column of that tap exists
             if constexpr (CONV) {
-                const int pix = tok0 / p.Bp;
-                nn = tok0 - pix * p.Bp;
-                ho = (pix / p.Wo) * p.stride - (p.R >> 1);
-                wo = (pix % p.Wo) * p.stride - (p.S >> 1);
+                const int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
+                const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                const int hb = oh * p.stride - (p.R >> 1), wb = ow * p.stride - (p.S >> 1);
+                if (chunk_ok) {
+                    for (int r = 0; r < p.R; ++r) hmask |= (uint32_t)((unsigned)(hb + r) < (unsigned)p.Hin) << r;
+                    for (int t = 0; t < p.S; ++t) wmask |= (uint32_t)((unsigned)(wb + t) < (unsigned)p.Win) << t;
+                }
+                base_off = (hb * p.Win + wb) * p.Bp + nn;
             }
             const __half* lane_src0 = chunk_ok ? p.B + tok0 : p.B;   // SpMM: column tok0 of row 0
             const size_t row_pitch = chunk_ok ? (size_t)p.N : 0;      // out-of-range chunks read B[0] with size 0
@@ -305,22 +312,25 @@ panel_umma_kernel(const PanelParams p) {
                                                lane_src0 + (size_t)ids[rbase + q * RPI] * row_pitch, nbytes);
                     }
                 } else {
-                    // lane j < RPW decodes (c, r, s) of row pw*RPW + j once; the others get it by shuffle
-                    const int k = ids[pw * RPW + (lane % RPW)];
-                    const int c = k % p.Cin, rs = k / p.Cin;
-                    const int coff = c * p.Hin * p.Win, rs_pack = ((rs / p.S) << 8) | (rs % p.S);
-#pragma unroll
+                    // Column ids arrive decoded (c | r << 16 | s << 24).  Lane j < RPW turns row
+                    // pw*RPW + j into an offset once; the copy loop fetches it by shuffle.  The loop
+                    // is kept rolled: the roles share a small instruction cache and a long
+                    // straight-line body costs more in fetch stalls than the loop overhead.
+                    const int idv = ids[pw * RPW + (lane % RPW)];
+                    const int tr = (idv >> 16) & 0xff, ts = (idv >> 24) & 0xff;
+                    const int delta = ((idv & 0xffff) * (p.Hin * p.Win) + tr * p.Win + ts) * p.Bp;
+                    const int rs_pack = tr | (ts << 8);
+                    const int nrow = rows_valid - rbase;   // copies with q * RPI < nrow are inside the block
+#pragma unroll 2
                     for (int q = 0; q < NQ; ++q) {
-                        const int src_lane = q * RPI + sub;
-                        const int kk = __shfl_sync(0xffffffffu, coff, src_lane);
-                        const int rsq = __shfl_sync(0xffffffffu, rs_pack, src_lane);
-                        if (rbase + q * RPI < rows_valid && !(ablate & 2)) {
-                            const int hi = ho + (rsq >> 8), wi = wo + (rsq & 0xff);
-                            const bool ok = chunk_ok && hi >= 0 && hi < p.Hin && wi >= 0 && wi < p.Win;
-                            const __half* src = ok ? p.Xs + ((size_t)(kk + hi * p.Win + wi) * p.Bp + nn) : p.Xs;
-                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT], src,
-                                               ok ? 16u : 0u);
-                        }
+                        const int row = q * RPI + sub;      // row of this warp's slice
+                        const int dq = __shfl_sync(0xffffffffu, delta, row);
+                        const int rsq = __shfl_sync(0xffffffffu, rs_pack, row);
+                        const bool ok = ((hmask >> (rsq & 0xff)) & (wmask >> (rsq >> 8)) & 1u) != 0;
+                        const int r7 = row & 7;
+                        if (q * RPI < nrow && !(ablate & 2))
+                            sm100::cp_async_16(st_base + gbase + (uint32_t)((row >> 3) * 2048 + r7 * 128 + (((chunk & 7) ^ r7) << 4)),
+                                               ok ? p.Xs + (base_off + dq) : p.Xs, ok ? 16u : 0u);
                     }
                 }
                 // Value panel slice [rows_valid][V]: contiguous in global memory.

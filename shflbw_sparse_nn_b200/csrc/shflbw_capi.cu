@@ -126,7 +126,7 @@ void drop_device_copy(shflbw_matrix& m) {
     void** bufs[] = {&m.d_meta, &m.d_val, &m.stage_in, &m.stage_c, &m.stage_out, &m.conv_in, &m.conv_out};
     for (void** b : bufs) if (*b) { cudaFree(*b); *b = nullptr; }
     m.stage_in_bytes = m.stage_c_bytes = m.stage_out_bytes = m.conv_in_bytes = m.conv_out_bytes = 0;
-    m.d_kptr = m.d_kidx = m.d_perm = nullptr;
+    m.d_kptr = m.d_kidx = m.d_perm = m.d_kcrs = nullptr;
     m.d_status = nullptr;
     m.device = -1;
 }
@@ -146,11 +146,13 @@ int shflbw_matrix_to_device(shflbw_matrix_t* m) {
     CK(cudaGetDevice(&dev));
     auto up8 = [](size_t v) { return (v + 7) / 8 * 8; };
     const size_t o_ptr = 0, o_idx = up8(m->kptr.size()), o_perm = o_idx + up8(m->kidx.size()),
-                 o_stat = o_perm + up8(m->row_permute_ids.size()), total = o_stat + 8;
+                 o_crs = o_perm + up8(m->row_permute_ids.size()), o_stat = o_crs + up8(m->kcrs.size()),
+                 total = o_stat + 8;
     std::vector<int> img(total, 0);
     std::copy(m->kptr.begin(), m->kptr.end(), img.begin() + o_ptr);
     std::copy(m->kidx.begin(), m->kidx.end(), img.begin() + o_idx);
     std::copy(m->row_permute_ids.begin(), m->row_permute_ids.end(), img.begin() + o_perm);
+    std::copy(m->kcrs.begin(), m->kcrs.end(), img.begin() + o_crs);
     CK(cudaMalloc(&m->d_meta, total * sizeof(int)));
     if (!cuda_ok(cudaMalloc(&m->d_val, m->kval.size() * 2), "cudaMalloc(values)")) {
         cudaFree(m->d_meta); m->d_meta = nullptr;
@@ -162,6 +164,7 @@ int shflbw_matrix_to_device(shflbw_matrix_t* m) {
     m->d_kptr = base + o_ptr;
     m->d_kidx = base + o_idx;
     m->d_perm = m->row_permute ? base + o_perm : nullptr;
+    m->d_kcrs = m->kcrs.empty() ? nullptr : base + o_crs;
     m->d_status = (int*)m->d_meta + o_stat;
     m->device = dev;
     return SHFLBW_OK;
@@ -281,6 +284,10 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
 
 // ---------------------------------------------------------------------------- SpConv --
 
+// Dynamic shared memory of unpermute_filters: the permutation (4 bytes per filter) plus one
+// F-vector of fp16 per warp (8 warps).
+static size_t unperm_smem_bytes(int F) { return (size_t)F * 4 + (size_t)F * 16; }
+
 int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap,
                        void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
     if (!out) return SHFLBW_ERR_INVALID_ARG;
@@ -295,15 +302,19 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
     const int Bp = (B + 7) / 8 * 8;
     const long long tokens = (long long)Ho * Wo * Bp;
-    if ((long long)f->C * Hin * Win >= (1ll << 31) / 1 || tokens >= (1ll << 31) ||
-        (long long)f->C * Hin * Win * Bp >= (1ll << 40))
-        return SHFLBW_ERR_UNSUPPORTED;
+    // 32-bit element offsets into the staged input.
+    if (tokens >= (1ll << 31) || (long long)f->C * Hin * Win * Bp >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
 
     out->B = B; out->Hin = Hin; out->Win = Win; out->C = f->C; out->F = f->F; out->R = f->R; out->S = f->S;
     out->stride = stride; out->Ho = Ho; out->Wo = Wo; out->V = f->brow; out->Bp = Bp;
     out->alpha = alpha; out->ifmap = ifmap; out->ofmap = ofmap;
     out->blk_ptr = f->d_kptr; out->blk_idx = f->d_kidx; out->blk_val = f->d_val;
     out->perm = f->d_perm; out->status_word = f->d_status;
+    if (kernel != SHFLBW_KERNEL_SIMT) {
+        // The panel kernel reads decoded column ids and keeps tap validity in 32-bit masks.
+        if (!f->d_kcrs || f->R > 32 || f->S > 32) return SHFLBW_ERR_UNSUPPORTED;
+        out->blk_idx = f->d_kcrs;
+    }
     if (kernel == SHFLBW_KERNEL_SIMT) {
         out->kernel = SHFLBW_KERNEL_SIMT;
         out->block_x = 128; out->grid_x = (f->F + 127) / 128; out->grid_y = (unsigned)(B * Ho * Wo);
@@ -330,9 +341,10 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
         out->staged_out_bytes = (size_t)B * Ho * Wo * f->F * 2;
         if ((rc = ensure_buffer(&f->conv_out, &f->conv_out_bytes, out->staged_out_bytes)) != SHFLBW_OK) return rc;
         out->staged_out = f->conv_out;
-        if ((size_t)f->F * 16 > 48 * 1024)
+        if (unperm_smem_bytes(f->F) > 227 * 1024) return SHFLBW_ERR_UNSUPPORTED;
+        if (unperm_smem_bytes(f->F) > 48 * 1024)
             CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, f->F * 16));
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)unperm_smem_bytes(f->F)));
     }
     out->init_success = 1;
     return SHFLBW_OK;
@@ -370,13 +382,17 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     p.Bn = st->B; p.Bp = st->Bp; p.Hin = st->Hin; p.Win = st->Win; p.Cin = st->C; p.F = st->F;
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
     p.num_items = st->num_items; p.tiles_n = st->tiles_n;
+#ifdef SHFLBW_ABLATE
+    if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
+    if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
+#endif
     ch.fn<<<dim3(st->grid_x, st->grid_y), st->block_x, st->shared_mem_size, s>>>(p);
     // 3. inverse filter permutation.
     if (st->staged_out) {
         const int num_pos = st->B * st->Ho * st->Wo;
         int blocks = (num_pos + 7) / 8;
         if (blocks > 148 * 8) blocks = 148 * 8;
-        shflbw::unpermute_filters<<<blocks, 256, (size_t)st->F * 16, s>>>(
+        shflbw::unpermute_filters<<<blocks, 256, unperm_smem_bytes(st->F), s>>>(
             (const __half*)st->staged_out, (__half*)st->ofmap, st->perm, num_pos, st->F);
     }
     CK(cudaGetLastError());
@@ -422,6 +438,7 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     const int Bp = (B + 7) / 8 * 8;
     const long long tokens = (long long)Ho * Wo * Bp;
     if ((long long)f->C * Hin * Win >= (1ll << 31) || tokens >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+    if (!f->d_kcrs || f->R > 32 || f->S > 32) return SHFLBW_ERR_UNSUPPORTED;
 
     // Capacity check first: nothing is launched when the shape does not fit.
     auto up256 = [](unsigned long long v) { return (v + 255ull) / 256ull * 256ull; };
@@ -466,11 +483,12 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     st.staged_in = scratch; st.staged_in_bytes = (size_t)in_bytes;
     if (f->row_permute) {
         st.staged_out = scratch + in_bytes; st.staged_out_bytes = (size_t)out_bytes;
-        if ((size_t)f->F * 16 > 48 * 1024)
+        if (unperm_smem_bytes(f->F) > 227 * 1024) return SHFLBW_ERR_UNSUPPORTED;
+        if (unperm_smem_bytes(f->F) > 48 * 1024)
             CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, f->F * 16));
+                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)unperm_smem_bytes(f->F)));
     }
-    st.blk_ptr = f->d_kptr; st.blk_idx = f->d_kidx; st.blk_val = f->d_val;
+    st.blk_ptr = f->d_kptr; st.blk_idx = f->d_kcrs; st.blk_val = f->d_val;
     st.perm = f->d_perm; st.status_word = f->d_status;
     st.init_success = 1;
     return shflbw_spconv_exec(&st, stream);

@@ -134,9 +134,9 @@ void build_host_images(shflbw_matrix& m) {
 
     // Kernel image: per row block, column list padded to a multiple of kShflbwKPad.  A
     // padding column repeats the block's last real column (a valid, already-fetched row of
-    // the dense operand) and carries zero values, so it contributes exactly 0.  Sixteen
-    // trailing zero panels follow the last block so a full-stage read past the end stays
-    // inside the allocation.
+    // the dense operand) and carries zero values, so it contributes exactly 0.  256 slack
+    // rows (zero values, column 0) follow the last block so a full-stage read past the end
+    // stays inside the allocation.
     m.kptr.assign(X + 1, 0);
     size_t rows = 0;
     for (int i = 0; i < X; ++i) {
@@ -155,6 +155,16 @@ void build_host_images(shflbw_matrix& m) {
             std::memcpy(&m.kval[r * m.brow], &m.values[(size_t)p * m.brow], (size_t)m.brow * 2);
         }
         for (; r < (size_t)m.kptr[i + 1]; ++r) m.kidx[r] = e > b ? m.indices[e - 1] : 0;
+    }
+    // Filters: the implicit-GEMM gather wants (channel, tap row, tap column) of every column
+    // id; decoding once here removes three integer divisions per row from the kernel.
+    m.kcrs.clear();
+    if (m.is_filter && m.C > 0 && m.C < 65536 && m.R < 256 && m.S < 256) {
+        m.kcrs.resize(m.kidx.size());
+        for (size_t r = 0; r < m.kidx.size(); ++r) {
+            const int k = m.kidx[r], c = k % m.C, rs = k / m.C;
+            m.kcrs[r] = c | ((rs / m.S) << 16) | ((rs % m.S) << 24);
+        }
     }
 }
 

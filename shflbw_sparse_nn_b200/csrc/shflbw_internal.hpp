@@ -28,14 +28,16 @@ struct shflbw_matrix {
     // ---- host images ----
     std::vector<int> meta_h;       // reference-compatible [indptr | indices*bcol | perm], pad 8
     std::vector<int> kptr, kidx;   // kernel image: padded offsets / column ids
+    std::vector<int> kcrs;         // filters only: kidx decoded as c | r << 16 | s << 24 (k = (r*S + s)*C + c)
     std::vector<uint16_t> kval;    // kernel image: padded fp16 panels [rows][brow]
 
     // ---- device copy (owned) ----
     int device = -1;
-    void* d_meta = nullptr;        // one int32 allocation: kptr | kidx | perm | status word
+    void* d_meta = nullptr;        // one int32 allocation: kptr | kidx | perm | kcrs | status word
     void* d_val = nullptr;
     const int* d_kptr = nullptr;
     const int* d_kidx = nullptr;
+    const int* d_kcrs = nullptr;   // filters with C < 65536 and R, S < 256 only
     const int* d_perm = nullptr;
     int* d_status = nullptr;
 
