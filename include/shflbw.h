@@ -209,7 +209,7 @@ typedef struct shflbw_spconv_state {
     float alpha;
     const void* ifmap;       /* NHWC input (device)  */
     void* ofmap;             /* NHWC output (device) */
-    void* staged_in;         /* scratch: input re-laid as [C][Hin][Win][Bp]            */
+    void* staged_in;         /* scratch: input as [C][Hin+R-1][Win+S-1][Bp], zero halo */
     void* staged_out;        /* scratch: [B*Ho*Wo][F] in stored filter order, or NULL  */
     size_t staged_in_bytes, staged_out_bytes;
     const int* blk_ptr;
@@ -249,8 +249,8 @@ int shflbw_spconv_host(shflbw_matrix_t* filter, int B, int Hin, int Win, int str
  *  - `filter` must already be on the device (shflbw_matrix_to_device, done at set-up time).
  *  - ifmap / ofmap are NHWC device pointers exactly as for shflbw_spconv_init; the launch is
  *    asynchronous on `stream`.
- *  - Needs 2*C*Hin*Win*roundup8(B) bytes, plus 2*B*Ho*Wo*F when the filter is permuted, each
- *    rounded up to 256.  More than the capacity -> SHFLBW_ERR_TOO_LARGE, nothing is launched.
+ *  - Needs 2*C*(Hin+R-1)*(Win+S-1)*roundup8(B) bytes, plus 2*B*Ho*Wo*F when the filter is
+ *    permuted, each rounded up to 256.  More than the capacity -> SHFLBW_ERR_TOO_LARGE, nothing is launched.
  *  - The first call on each device looks up the array's device address; make that first
  *    call during set-up, before any stream capture on that device.
  *  - All calls on a device share the one array and it keeps the previous call's contents.

@@ -14,18 +14,23 @@
 
 namespace shflbw {
 
-// in[n][p][c] (NHWC, p = hi*Win + wi)  ->  Xs[c][p][Bp] with n < Bn copied and n >= Bn zero.
-// One block: 64 channels x 128 (pixel, image) slots, images fastest.  Both global accesses
-// are 16 bytes per thread (8 channels in, 8 images out); the transpose happens in shared
-// memory, whose 8-slot groups are XOR-swizzled by the channel group so that neither the
-// 2-byte scatter nor the 16-byte read-back has bank conflicts.  Requires C % 8 == 0, Bp % 8 == 0.
+// in[n][hi][wi][c] (NHWC)  ->  Xs[c][hp][wp][Bp], the channel-major, batch-innermost staging
+// buffer with a zero halo: hp = hi + ph in [0, Hp), wp = wi + pw in [0, Wp); images n >= Bn and
+// halo pixels are written as zero, so every filter tap of every output pixel reads a valid
+// address and the gather needs no bounds logic.
+// One block: 64 channels x 128 (padded pixel, image) slots, images fastest.  Both global
+// accesses are 16 bytes per thread (8 channels in, 8 images out); the transpose happens in
+// shared memory, whose 8-slot groups are XOR-swizzled by the channel group so that neither
+// the 2-byte scatter nor the 16-byte read-back has bank conflicts.  C % 8 == 0, Bp % 8 == 0.
 constexpr int kRelayoutC = 64, kRelayoutSlots = 128;
 __global__ void __launch_bounds__(256)
-relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, int Bn, int Bp, int P, int C) {
+relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, int Bn, int Bp, int Hin, int Win,
+                      int Hp, int Wp, int ph, int pw, int C) {
     __shared__ __align__(16) __half tile[kRelayoutC * kRelayoutSlots];
     const int NT = Bp < 32 ? Bp : 32;        // images per tile (a multiple of 8)
-    const int PT = kRelayoutSlots / NT;      // pixels per tile
+    const int PT = kRelayoutSlots / NT;      // padded pixels per tile
     const int n_tiles = (Bp + NT - 1) / NT;
+    const int PP = Hp * Wp;
     const int p0 = (blockIdx.x / n_tiles) * PT, nb = (blockIdx.x % n_tiles) * NT;
     const int c0 = blockIdx.y * kRelayoutC;
     // load: thread -> (slot, 8-channel chunk), chunk fastest: 8 lanes read 128 contiguous bytes
@@ -36,9 +41,11 @@ relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, in
         const int chunk = e & 7, slot = e >> 3;
         const int pl = slot / NT, nl = slot - pl * NT;
         const int pp = p0 + pl, n = nb + nl;
+        const int hp = pp / Wp, hi = hp - ph, wi = pp - hp * Wp - pw;
         v[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (pl < PT && pp < P && n < Bn && c0 + chunk * 8 < C)
-            v[i] = __ldg((const uint4*)(in + ((size_t)n * P + pp) * C + c0 + chunk * 8));
+        if (pl < PT && pp < PP && n < Bn && c0 + chunk * 8 < C && (unsigned)hi < (unsigned)Hin &&
+            (unsigned)wi < (unsigned)Win)
+            v[i] = __ldg((const uint4*)(in + (((size_t)n * Hin + hi) * Win + wi) * C + c0 + chunk * 8));
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
@@ -58,8 +65,8 @@ relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, in
         const int slot = g * 8;
         const int pl = slot / NT, nl = slot - pl * NT;
         const int pp = p0 + pl, n = nb + nl;
-        if (pl < PT && pp < P && n < Bp && c0 + c < C)
-            *(uint4*)(Xs + ((size_t)(c0 + c) * P + pp) * Bp + n) =
+        if (pl < PT && pp < PP && n < Bp && c0 + c < C)
+            *(uint4*)(Xs + ((size_t)(c0 + c) * PP + pp) * Bp + n) =
                 *(const uint4*)(tile + c * kRelayoutSlots + ((g ^ (c >> 3)) << 3));
     }
 }

@@ -63,10 +63,11 @@ struct PanelParams {
     const __half* C;         // [M][N] or nullptr
     __half* D;               // [M][N]
     int N;                   // dense columns (SpMM) / Ho*Wo*Bp (SpConv)
-    // SpConv (input staged channel-major, batch innermost: Xs[c][hi][wi][Bp])
+    // SpConv (input staged channel-major, batch innermost, with a zero halo:
+    // Xs[c][Hp][Wp][Bp], Hp = Hin + R - 1, Wp = Win + S - 1, image origin at (R/2, S/2))
     const __half* Xs;
     __half* out;             // [B*Ho*Wo][F] (NHWC) -- final or staged in stored filter order
-    int Bn, Bp, Hin, Win, Cin, F, R, S, stride, Ho, Wo;
+    int Bn, Bp, Hp, Wp, Cin, F, R, S, stride, Ho, Wo;
 };
 
 template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
@@ -270,19 +271,15 @@ panel_umma_kernel(const PanelParams p) {
             const int tok0 = (item % p.tiles_n) * T + chunk * 8;
             const bool chunk_ok = tok0 < p.N;
             const uint32_t nbytes = chunk_ok ? 16u : 0u;
-            // SpConv: this lane's 8 tokens are 8 images of one output pixel.  Which filter taps
-            // (r, s) fall inside the input is a per-item property of the lane: two bit masks.
-            int base_off = 0;                  // staged-input offset of tap (0, 0), may be negative
-            uint32_t hmask = 0, wmask = 0;     // bit r / bit s: input row / column of that tap exists
+            // SpConv: this lane's 8 tokens are 8 images of one output pixel; the staged input
+            // has a zero halo, so tap (r, s) of that pixel is simply base + ((r*Wp + s) * Bp).
+            const __half* conv_src0 = p.Xs;
             if constexpr (CONV) {
-                const int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
-                const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
-                const int hb = oh * p.stride - (p.R >> 1), wb = ow * p.stride - (p.S >> 1);
                 if (chunk_ok) {
-                    for (int r = 0; r < p.R; ++r) hmask |= (uint32_t)((unsigned)(hb + r) < (unsigned)p.Hin) << r;
-                    for (int t = 0; t < p.S; ++t) wmask |= (uint32_t)((unsigned)(wb + t) < (unsigned)p.Win) << t;
+                    const int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
+                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                    conv_src0 = p.Xs + ((oh * p.stride * p.Wp + ow * p.stride) * p.Bp + nn);
                 }
-                base_off = (hb * p.Win + wb) * p.Bp + nn;
             }
             const __half* lane_src0 = chunk_ok ? p.B + tok0 : p.B;   // SpMM: column tok0 of row 0
             const size_t row_pitch = chunk_ok ? (size_t)p.N : 0;      // out-of-range chunks read B[0] with size 0
@@ -313,24 +310,15 @@ panel_umma_kernel(const PanelParams p) {
                     }
                 } else {
                     // Column ids arrive decoded (c | r << 16 | s << 24).  Lane j < RPW turns row
-                    // pw*RPW + j into an offset once; the copy loop fetches it by shuffle.  The loop
-                    // is kept rolled: the roles share a small instruction cache and a long
-                    // straight-line body costs more in fetch stalls than the loop overhead.
+                    // pw*RPW + j into an element offset once; the copies fetch it by shuffle.
                     const int idv = ids[pw * RPW + (lane % RPW)];
-                    const int tr = (idv >> 16) & 0xff, ts = (idv >> 24) & 0xff;
-                    const int delta = ((idv & 0xffff) * (p.Hin * p.Win) + tr * p.Win + ts) * p.Bp;
-                    const int rs_pack = tr | (ts << 8);
-                    const int nrow = rows_valid - rbase;   // copies with q * RPI < nrow are inside the block
-#pragma unroll 2
+                    const int delta = ((idv & 0xffff) * (p.Hp * p.Wp) + ((idv >> 16) & 0xff) * p.Wp + ((idv >> 24) & 0xff)) * p.Bp;
+#pragma unroll
                     for (int q = 0; q < NQ; ++q) {
-                        const int row = q * RPI + sub;      // row of this warp's slice
-                        const int dq = __shfl_sync(0xffffffffu, delta, row);
-                        const int rsq = __shfl_sync(0xffffffffu, rs_pack, row);
-                        const bool ok = ((hmask >> (rsq & 0xff)) & (wmask >> (rsq >> 8)) & 1u) != 0;
-                        const int r7 = row & 7;
-                        if (q * RPI < nrow && !(ablate & 2))
-                            sm100::cp_async_16(st_base + gbase + (uint32_t)((row >> 3) * 2048 + r7 * 128 + (((chunk & 7) ^ r7) << 4)),
-                                               ok ? p.Xs + (base_off + dq) : p.Xs, ok ? 16u : 0u);
+                        const int dq = __shfl_sync(0xffffffffu, delta, q * RPI + sub);
+                        if (rbase + q * RPI < rows_valid && !(ablate & 2))
+                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
+                                               conv_src0 + dq, nbytes);
                     }
                 }
                 // Value panel slice [rows_valid][V]: contiguous in global memory.

@@ -302,8 +302,9 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
     const int Bp = (B + 7) / 8 * 8;
     const long long tokens = (long long)Ho * Wo * Bp;
-    // 32-bit element offsets into the staged input.
-    if (tokens >= (1ll << 31) || (long long)f->C * Hin * Win * Bp >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+    // 32-bit element offsets into the staged (halo-padded) input.
+    const long long staged_elems = (long long)f->C * (Hin + f->R - 1) * (Win + f->S - 1) * Bp;
+    if (tokens >= (1ll << 31) || staged_elems >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
 
     out->B = B; out->Hin = Hin; out->Win = Win; out->C = f->C; out->F = f->F; out->R = f->R; out->S = f->S;
     out->stride = stride; out->Ho = Ho; out->Wo = Wo; out->V = f->brow; out->Bp = Bp;
@@ -311,8 +312,8 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     out->blk_ptr = f->d_kptr; out->blk_idx = f->d_kidx; out->blk_val = f->d_val;
     out->perm = f->d_perm; out->status_word = f->d_status;
     if (kernel != SHFLBW_KERNEL_SIMT) {
-        // The panel kernel reads decoded column ids and keeps tap validity in 32-bit masks.
-        if (!f->d_kcrs || f->R > 32 || f->S > 32) return SHFLBW_ERR_UNSUPPORTED;
+        // The panel kernel reads decoded column ids (channel in 16 bits, taps in 8 bits each).
+        if (!f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
         out->blk_idx = f->d_kcrs;
     }
     if (kernel == SHFLBW_KERNEL_SIMT) {
@@ -334,7 +335,7 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     out->grid_x = persistent_grid(out->num_items, sms); out->grid_y = 1;
     out->shared_mem_size = ch.smem;
     // Scratch owned by the filter handle, grown on demand.
-    out->staged_in_bytes = (size_t)f->C * Hin * Win * Bp * 2;
+    out->staged_in_bytes = (size_t)staged_elems * 2;
     if ((rc = ensure_buffer(&f->conv_in, &f->conv_in_bytes, out->staged_in_bytes)) != SHFLBW_OK) return rc;
     out->staged_in = f->conv_in;
     if (f->row_permute) {
@@ -363,14 +364,15 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     }
     PanelChoice ch;
     if (!lookup_pw<true>(st->V, st->tokens_per_cta, st->producer_warps, st->variant, &ch)) return SHFLBW_ERR_INVALID_ARG;
-    // 1. NHWC -> channel-major, batch-innermost staging.
+    // 1. NHWC -> channel-major, batch-innermost staging with a zero halo.
+    const int Hp = st->Hin + st->R - 1, Wp = st->Win + st->S - 1;
     {
-        const int P = st->Hin * st->Win;
+        const int PP = Hp * Wp;
         const int NT = st->Bp < 32 ? st->Bp : 32, PT = shflbw::kRelayoutSlots / NT;
         const int n_tiles = (st->Bp + NT - 1) / NT;
-        dim3 grid((unsigned)(((P + PT - 1) / PT) * n_tiles), (unsigned)((st->C + shflbw::kRelayoutC - 1) / shflbw::kRelayoutC));
-        shflbw::relayout_nhwc_to_chwn<<<grid, 256, 0, s>>>((const __half*)st->ifmap, (__half*)st->staged_in,
-                                                           st->B, st->Bp, P, st->C);
+        dim3 grid((unsigned)(((PP + PT - 1) / PT) * n_tiles), (unsigned)((st->C + shflbw::kRelayoutC - 1) / shflbw::kRelayoutC));
+        shflbw::relayout_nhwc_to_chwn<<<grid, 256, 0, s>>>((const __half*)st->ifmap, (__half*)st->staged_in, st->B,
+                                                           st->Bp, st->Hin, st->Win, Hp, Wp, st->R / 2, st->S / 2, st->C);
     }
     // 2. implicit-GEMM panel kernel.
     shflbw::PanelParams p{};
@@ -379,7 +381,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     p.N = st->Ho * st->Wo * st->Bp;
     p.Xs = (const __half*)st->staged_in;
     p.out = (__half*)(st->staged_out ? st->staged_out : st->ofmap);
-    p.Bn = st->B; p.Bp = st->Bp; p.Hin = st->Hin; p.Win = st->Win; p.Cin = st->C; p.F = st->F;
+    p.Bn = st->B; p.Bp = st->Bp; p.Hp = Hp; p.Wp = Wp; p.Cin = st->C; p.F = st->F;
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
     p.num_items = st->num_items; p.tiles_n = st->tiles_n;
 #ifdef SHFLBW_ABLATE
@@ -438,11 +440,11 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     const int Bp = (B + 7) / 8 * 8;
     const long long tokens = (long long)Ho * Wo * Bp;
     if ((long long)f->C * Hin * Win >= (1ll << 31) || tokens >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
-    if (!f->d_kcrs || f->R > 32 || f->S > 32) return SHFLBW_ERR_UNSUPPORTED;
+    if (!f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
 
     // Capacity check first: nothing is launched when the shape does not fit.
     auto up256 = [](unsigned long long v) { return (v + 255ull) / 256ull * 256ull; };
-    const unsigned long long in_bytes = up256(2ull * f->C * Hin * Win * Bp);
+    const unsigned long long in_bytes = up256(2ull * f->C * (Hin + f->R - 1) * (Win + f->S - 1) * Bp);
     const unsigned long long out_bytes = f->row_permute ? up256(2ull * B * Ho * Wo * f->F) : 0ull;
     if (in_bytes + out_bytes > (unsigned long long)SHFLBW_STATIC_SCRATCH_BYTES) {
         snprintf(g_cuda_err, sizeof g_cuda_err,
