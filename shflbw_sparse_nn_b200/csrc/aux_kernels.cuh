@@ -72,28 +72,30 @@ relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, in
 }
 
 // out[q][perm[f]] = staged[q][f] for every output position q; one warp per position.  The
-// permutation sits in shared memory (read once per block); each lane moves 8 filters at a
-// time with 16-byte global accesses and scatters them into the warp's F-vector in shared
-// memory with 2-byte stores.  Dynamic shared memory: F*4 bytes (perm) + 8*F*2 bytes.  F % 8 == 0.
-__global__ void __launch_bounds__(256)
+// permutation sits in shared memory as 16-bit ids (read once per block); each lane moves 8
+// filters at a time with 16-byte global accesses and scatters them into the warp's F-vector
+// in shared memory with 2-byte stores.  Dynamic shared memory: F*2 bytes (perm) + warps*F*2
+// bytes.  F % 8 == 0, F <= 65536.
+constexpr int kUnpermWarps = 8;
+__global__ void __launch_bounds__(kUnpermWarps * 32)
 unpermute_filters(const __half* __restrict__ staged, __half* __restrict__ out, const int* __restrict__ perm,
                   int num_pos, int F) {
     extern __shared__ __align__(16) uint8_t unperm_smem[];
-    int* sperm = (int*)unperm_smem;                          // [F]
-    __half* vec = (__half*)(unperm_smem + (size_t)F * 4);     // [8 warps][F]
+    unsigned short* sperm = (unsigned short*)unperm_smem;        // [F]
+    __half* vec = (__half*)(unperm_smem + (size_t)F * 2);        // [warps][F]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int f = threadIdx.x; f < F; f += 256) sperm[f] = __ldg(perm + f);
+    for (int f = threadIdx.x; f < F; f += kUnpermWarps * 32) sperm[f] = (unsigned short)__ldg(perm + f);
     __syncthreads();
     __half* mine = vec + (size_t)warp * F;
-    for (int q = blockIdx.x * 8 + warp; q < num_pos; q += gridDim.x * 8) {
+    for (int q = blockIdx.x * kUnpermWarps + warp; q < num_pos; q += gridDim.x * kUnpermWarps) {
         const __half* src = staged + (size_t)q * F;
 #pragma unroll 4
         for (int f8 = lane * 8; f8 < F; f8 += 256) {
             const uint4 v = *(const uint4*)(src + f8);
-            const int4 pa = *(const int4*)(sperm + f8), pb = *(const int4*)(sperm + f8 + 4);
+            const uint4 pp = *(const uint4*)(sperm + f8);
             const __half* h = (const __half*)&v;
-            mine[pa.x] = h[0]; mine[pa.y] = h[1]; mine[pa.z] = h[2]; mine[pa.w] = h[3];
-            mine[pb.x] = h[4]; mine[pb.y] = h[5]; mine[pb.z] = h[6]; mine[pb.w] = h[7];
+            mine[pp.x & 0xffff] = h[0]; mine[pp.x >> 16] = h[1]; mine[pp.y & 0xffff] = h[2]; mine[pp.y >> 16] = h[3];
+            mine[pp.z & 0xffff] = h[4]; mine[pp.z >> 16] = h[5]; mine[pp.w & 0xffff] = h[6]; mine[pp.w >> 16] = h[7];
         }
         __syncwarp();
         __half* dst = out + (size_t)q * F;

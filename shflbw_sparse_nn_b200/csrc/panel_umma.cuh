@@ -80,7 +80,9 @@ struct PanelCfg {
     static constexpr int W_BYTES = KS * V * 2;
     static constexpr int STAGE_BYTES = G_BYTES + W_BYTES;
     static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
-    static constexpr int OUT_BYTES = 0;                     // the epilogue stores straight from registers
+    // SpConv: each epilogue warp transposes 32 positions x 32 filters through 2 KB so that its
+    // global stores are 64-byte runs; the SpMM epilogue stores straight from registers.
+    static constexpr int OUT_BYTES = CONV ? 8 * 2048 : 0;
     static constexpr int BAR_BYTES = (STAGES * 2 + 8) * 8;   // mbarriers + tmem slot + abort flag
     static constexpr int TAB_BYTES = 512 * 8;               // per-CTA item table (kPanelMaxItemsPerCta entries)
     static constexpr int IDX_RING = 8;                      // stages of row ids kept in shared memory
@@ -458,14 +460,19 @@ panel_umma_kernel(const PanelParams p) {
             const int mbase = col0 % V;                    // first block row / filter of this warp
             bool ok = tok < p.N && !(ablate & 8);
             uint32_t my_off = 0;                           // SpMM: row offset of block row mbase + 32*g + lane
-            __half* dst = nullptr;                         // SpConv: this position's F-vector at the block's filters
+            uint32_t row_off[4];                           // SpConv: output offsets of positions i*8 + lane/4
             if constexpr (CONV) {
                 const int pix = tok / p.Bp, img = tok - pix * p.Bp;
                 ok = ok && img < p.Bn;
                 const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
-                dst = p.out + ((size_t)(img * p.Ho + oh) * p.Wo + ow) * p.F + blk * V + mbase;
+                // this position's F-vector at the block's filters (element offset; host checks it fits 32 bits)
+                const uint32_t mine = ok ? (uint32_t)((img * p.Ho + oh) * p.Wo + ow) * (uint32_t)p.F + (uint32_t)(blk * V + mbase)
+                                         : 0xffffffffu;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) row_off[i] = __shfl_sync(0xffffffffu, mine, i * 8 + (lane >> 2));
             }
             const bool use_c = p.beta != 0.0f && p.C != nullptr;
+            if constexpr (!CONV) {
 #pragma unroll 1   // a short loop body: the three roles share a small instruction cache
             for (int c0 = 0; c0 < COLS; c0 += 8) {
                 uint32_t r[8];
@@ -483,7 +490,7 @@ panel_umma_kernel(const PanelParams p) {
                     if (tid == 0) TRACE(2, li, 1);
                 }
                 if (ablate & 512) continue;
-                if constexpr (!CONV) {
+                {
                     // Thread = token, registers = 8 output rows of the block.  For a fixed row the
                     // warp's 32 tokens are 64 contiguous bytes of D: one warp store per row straight
                     // from registers; the inverse row permutation is the row index of that store.
@@ -502,18 +509,52 @@ panel_umma_kernel(const PanelParams p) {
                             p.D[off] = h;
                         }
                     }
-                } else {
-                    // SpConv: thread = output position, registers = 8 consecutive filters of the
-                    // block, contiguous in the pixel's F-vector in stored filter order.
-                    if (ok) {
-                        uint4 v;
-                        __half2* h = (__half2*)&v;
+                }
+            }
+            } else {
+            // SpConv: thread = output position, accumulator columns = consecutive filters of the
+            // block, contiguous in the position's F-vector (stored filter order).  Straight from
+            // registers a warp store would touch 32 lines (one per position); instead each
+            // 32-filter chunk goes through a swizzled 2 KB tile so that four lanes write one
+            // position's 64 contiguous bytes.
+            uint8_t* my_tile = smem + Cfg::PIPE_BYTES + warp * 2048;
+#pragma unroll 1
+            for (int cc = 0; cc < COLS; cc += 32) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            h[e] = __hmul2(__floats2half2_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])), alpha2);
-                        *(uint4*)(dst + c0) = v;
+                for (int j = 0; j < 4; ++j) {
+                    const int c0 = cc + j * 8;
+                    uint32_t r[8];
+                    if (has_k && reads) {
+                        sm100::tmem_ld_32x32b_x8(acc_base + c0, r);
+                        sm100::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) r[e] = 0u;
+                    }
+                    if (c0 + 8 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
+                        sm100::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
+                        if (tid == 0) TRACE(2, li, 1);
+                    }
+                    uint4 v;
+                    __half2* h = (__half2*)&v;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e)
+                        h[e] = __hmul2(__floats2half2_rn(__uint_as_float(r[2 * e]), __uint_as_float(r[2 * e + 1])), alpha2);
+                    *(uint4*)(my_tile + lane * 64 + ((j ^ ((lane >> 1) & 3)) << 4)) = v;
+                }
+                __syncwarp();
+                if (!(ablate & 512)) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int row = i * 8 + (lane >> 2), c = lane & 3;
+                        const uint4 v = *(const uint4*)(my_tile + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
+                        if (row_off[i] != 0xffffffffu) *(uint4*)(p.out + (size_t)row_off[i] + cc + c * 8) = v;
                     }
                 }
+                __syncwarp();
+            }
             }
             if (tid == 0) TRACE(2, li, 3);
         }

@@ -90,9 +90,15 @@ int sm_count() {
 // SHFLBW_TILE=128|256 and SHFLBW_PW=8|16 override (tuning aids).
 template <bool CONV>
 int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
+    // Token tile: a persistent CTA works through ceil(items / SMs) items in turn; an item of
+    // the 128-token tile was measured at ~0.6x the time of a 256-token item (half the
+    // gathered bytes, the same number of pipeline stages).
     int tile = 256, pw = 8;
+    const int sms = sm_count() > 0 ? sm_count() : 148;
     const long long items256 = ((n_tokens + 255) / 256) * row_blocks;
-    if (items256 < 148 * 3) tile = 128;
+    const long long items128 = ((n_tokens + 127) / 128) * row_blocks;
+    const long long waves256 = (items256 + sms - 1) / sms, waves128 = (items128 + sms - 1) / sms;
+    if (n_tokens <= 128 || waves128 * 6 < waves256 * 10) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
     if (const char* e = getenv("SHFLBW_PW")) { int t = atoi(e); if (t == 8 || t == 16) pw = t; }
     int variant = 0;
@@ -284,9 +290,8 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
 
 // ---------------------------------------------------------------------------- SpConv --
 
-// Dynamic shared memory of unpermute_filters: the permutation (4 bytes per filter) plus one
-// F-vector of fp16 per warp (8 warps).
-static size_t unperm_smem_bytes(int F) { return (size_t)F * 4 + (size_t)F * 16; }
+// Dynamic shared memory of unpermute_filters: 16-bit permutation + one F-vector of fp16 per warp.
+static size_t unperm_smem_bytes(int F) { return (size_t)F * 2 * (1 + shflbw::kUnpermWarps); }
 
 int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap,
                        void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
@@ -305,6 +310,7 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     // 32-bit element offsets into the staged (halo-padded) input.
     const long long staged_elems = (long long)f->C * (Hin + f->R - 1) * (Win + f->S - 1) * Bp;
     if (tokens >= (1ll << 31) || staged_elems >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+    if ((long long)B * Ho * Wo * f->F >= (1ll << 32) - 1) return SHFLBW_ERR_UNSUPPORTED;  // 32-bit output offsets
 
     out->B = B; out->Hin = Hin; out->Win = Win; out->C = f->C; out->F = f->F; out->R = f->R; out->S = f->S;
     out->stride = stride; out->Ho = Ho; out->Wo = Wo; out->V = f->brow; out->Bp = Bp;
@@ -342,7 +348,7 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
         out->staged_out_bytes = (size_t)B * Ho * Wo * f->F * 2;
         if ((rc = ensure_buffer(&f->conv_out, &f->conv_out_bytes, out->staged_out_bytes)) != SHFLBW_OK) return rc;
         out->staged_out = f->conv_out;
-        if (unperm_smem_bytes(f->F) > 227 * 1024) return SHFLBW_ERR_UNSUPPORTED;
+        if (unperm_smem_bytes(f->F) > 227 * 1024 || f->F > 65536) return SHFLBW_ERR_UNSUPPORTED;
         if (unperm_smem_bytes(f->F) > 48 * 1024)
             CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)unperm_smem_bytes(f->F)));
@@ -392,9 +398,9 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     // 3. inverse filter permutation.
     if (st->staged_out) {
         const int num_pos = st->B * st->Ho * st->Wo;
-        int blocks = (num_pos + 7) / 8;
-        if (blocks > 148 * 8) blocks = 148 * 8;
-        shflbw::unpermute_filters<<<blocks, 256, unperm_smem_bytes(st->F), s>>>(
+        int blocks = (num_pos + shflbw::kUnpermWarps - 1) / shflbw::kUnpermWarps;
+        if (blocks > 148 * 6) blocks = 148 * 6;
+        shflbw::unpermute_filters<<<blocks, shflbw::kUnpermWarps * 32, unperm_smem_bytes(st->F), s>>>(
             (const __half*)st->staged_out, (__half*)st->ofmap, st->perm, num_pos, st->F);
     }
     CK(cudaGetLastError());
@@ -485,7 +491,7 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     st.staged_in = scratch; st.staged_in_bytes = (size_t)in_bytes;
     if (f->row_permute) {
         st.staged_out = scratch + in_bytes; st.staged_out_bytes = (size_t)out_bytes;
-        if (unperm_smem_bytes(f->F) > 227 * 1024) return SHFLBW_ERR_UNSUPPORTED;
+        if (unperm_smem_bytes(f->F) > 227 * 1024 || f->F > 65536) return SHFLBW_ERR_UNSUPPORTED;
         if (unperm_smem_bytes(f->F) > 48 * 1024)
             CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)unperm_smem_bytes(f->F)));
