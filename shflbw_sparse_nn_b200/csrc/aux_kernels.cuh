@@ -12,6 +12,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include "shflbw_internal.hpp"
+
 namespace shflbw {
 
 // in[n][hi][wi][c] (NHWC)  ->  Xs[c][hp][wp][Bp], the channel-major, batch-innermost staging
@@ -116,7 +118,7 @@ __global__ void simt_spmm(const int* __restrict__ blk_ptr, const int* __restrict
     const int blk = row / V, m = row % V;
     float acc = 0.f;
     for (int p = blk_ptr[blk]; p < blk_ptr[blk + 1]; ++p)
-        acc += __half2float(blk_val[(size_t)p * V + m]) * __half2float(B[(size_t)blk_idx[p] * N + n]);
+        acc += __half2float(blk_val[kval_index(V, (size_t)p, m)]) * __half2float(B[(size_t)blk_idx[p] * N + n]);
     const int dst = perm ? perm[row] : row;
     // Same epilogue arithmetic as the reference: round to fp16, then alpha / beta in fp16.
     __half h = __float2half_rn(acc), a = __float2half_rn(alpha);
@@ -141,7 +143,7 @@ __global__ void simt_spconv(const int* __restrict__ blk_ptr, const int* __restri
         const int c = k % Cin, s = (k / Cin) % S, r = (k / Cin) / S;
         const int hi = ho * stride - R / 2 + r, wi = wo * stride - S / 2 + s;
         if (hi < 0 || hi >= Hin || wi < 0 || wi >= Win) continue;
-        acc += __half2float(blk_val[(size_t)p * V + m]) *
+        acc += __half2float(blk_val[kval_index(V, (size_t)p, m)]) *
                __half2float(in[(((size_t)n * Hin + hi) * Win + wi) * Cin + c]);
     }
     const int dst = perm ? perm[f] : f;

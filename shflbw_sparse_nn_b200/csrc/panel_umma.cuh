@@ -74,7 +74,13 @@ template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
 struct PanelCfg {
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
-    static constexpr int THREADS = (9 + PW) * 32;
+    // Warp w runs on scheduler partition w % 4.  The MMA warp (8) sits on partition 0; with 8
+    // producer warps the block carries two idle warps (12, 16) so that no producer shares that
+    // partition -- the MMA warp executes a few dozen instructions per stage and was measured at
+    // ~20 clk per instruction when producer code kept evicting its lines from the partition's
+    // instruction cache.
+    static constexpr bool SPARE_P0 = PW == 8;
+    static constexpr int THREADS = SPARE_P0 ? 19 * 32 : (9 + PW) * 32;
     static constexpr int G_ACC = KS * 256;                 // gathered tile of one accumulator: [KS][128] fp16
     static constexpr int G_BYTES = TM * G_ACC;
     static constexpr int W_BYTES = KS * V * 2;
@@ -115,7 +121,7 @@ __device__ __forceinline__ uint32_t tile32_off(int r, int c) { return (uint32_t)
 constexpr int kPanelMaxItemsPerCta = 512;  // capacity of the per-CTA item table
 
 template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
-__global__ void __launch_bounds__((9 + PW) * 32, 1)
+__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, LAG_, PW, CONV>::THREADS, 1)
 panel_umma_kernel(const PanelParams p) {
     using Cfg = PanelCfg<V, TM, KS_, STAGES, LAG_, PW, CONV>;
     constexpr int KS = Cfg::KS, T = Cfg::T;
@@ -139,7 +145,9 @@ panel_umma_kernel(const PanelParams p) {
     const bool tracing = p.trace != nullptr && blockIdx.x == 0;
 #define TRACE(role, n, k) do { if (tracing && (n) < 256 && !(ablate & 256)) p.trace[(role) * 1024 + (n) * 4 + (k)] = now(); } while (0)
 #define CTRACE(k) do { if (p.trace != nullptr) p.trace[4096 + blockIdx.x * 8 + (k)] = now(); } while (0)
+#define PTRACE(w, n, k) do { if (tracing && (n) < 256 && !(ablate & 256)) p.trace[8192 + (w) * 1024 + (n) * 4 + (k)] = now(); } while (0)
 #else
+#define PTRACE(w, n, k) do { } while (0)
 #define CTRACE(k) do { } while (0)
     constexpr int ablate = 0;
 #define TRACE(role, n, k) do { } while (0)
@@ -180,7 +188,10 @@ panel_umma_kernel(const PanelParams p) {
     if (tid == 0) TRACE(3, 0, 0);
     if (tid == 0) CTRACE(1);
 
-    if (warp >= 9) {
+    const int pidx = Cfg::SPARE_P0 ? warp - 9 - (warp > 12) - (warp > 16) : warp - 9;   // producer number
+    if (Cfg::SPARE_P0 && (warp == 12 || warp == 16)) {
+        // idle: keeps producers off the MMA warp's scheduler partition
+    } else if (warp >= 9) {
         // ------------------------------------------------------------- producers ----
         // The PW producer warps form GROUPS groups that take the CTA's stages in turn (group g
         // fills stages g, g+GROUPS, ...).  While one group sits in its barrier round trip
@@ -193,14 +204,11 @@ panel_umma_kernel(const PanelParams p) {
         constexpr int CPR = T / 8;             // 16-byte chunks per gathered row
         constexpr int RPI = 32 / CPR;          // rows per warp instruction (TM=2: 1, TM=1: 2)
         constexpr int NQ = RPW / RPI;          // gather copies per lane per stage
-        constexpr int WCPR = V / 8;            // 16-byte chunks per value-panel row
-        constexpr int WQ = (KS * WCPR + GW * 32 - 1) / (GW * 32);  // value copies per thread per stage
         constexpr int XT = 8 / RPI;            // period of the swizzle term along q
         static_assert(RPW % 8 == 0, "a producer warp owns whole 8-row swizzle groups");
-        const int grp = (warp - 9) / GW, pw = (warp - 9) % GW;
+        const int grp = pidx / GW, pw = pidx % GW;
         const int chunk = lane % CPR;          // this lane's chunk of the token tile
         const int sub = RPI == 2 ? (lane >> 4) : 0;
-        const int ptid = pw * 32 + lane;
         // Everything that does not change from stage to stage is computed once.  Row q of this
         // lane is r = pw*RPW + q*RPI + sub; its swizzled offset splits into a lane constant, a
         // compile-time term in q and one of XT lane-dependent XOR terms.
@@ -212,16 +220,6 @@ panel_umma_kernel(const PanelParams p) {
             const int r7 = (j * RPI + sub) & 7;
             gx[j] = (uint32_t)(r7 * 128 + (((chunk & 7) ^ r7) << 4));
         }
-        int wrow[WQ];
-        uint32_t woff[WQ];
-#pragma unroll
-        for (int u = 0; u < WQ; ++u) {
-            const int q = ptid + u * GW * 32;
-            const int r = q / WCPR, c = q % WCPR;
-            wrow[u] = q < KS * WCPR ? r : KS;  // KS = never valid
-            woff[u] = (uint32_t)Cfg::G_BYTES + (V == 32 ? tile32_off(r, c) : V == 64 ? tile64_off(r, c) : tile128_off(r, c));
-        }
-
         // A cursor walks the flattened (item, stage) sequence of this CTA using the item table.
         struct Cursor { int li, kt, num_k, row_begin, rows_total; };
         auto enter = [&](Cursor& c) {           // position on the first stage of item c.li (skipping empty items)
@@ -284,8 +282,8 @@ panel_umma_kernel(const PanelParams p) {
                 }
             }
             const __half* lane_src0 = chunk_ok ? p.B + tok0 : p.B;   // SpMM: column tok0 of row 0
-            const size_t row_pitch = chunk_ok ? (size_t)p.N : 0;      // out-of-range chunks read B[0] with size 0
-            const __half* wsrc = p.blk_val + (size_t)ent.x * V + (size_t)ptid * 8;
+            const uint32_t row_pitch = chunk_ok ? (uint32_t)p.N : 0u;   // out-of-range chunks read B[0] with size 0
+            const __half* wsrc = p.blk_val + (size_t)ent.x * V;   // the block's value panel (stage kt at + kt*KS*V)
 
             for (int kt = 0; kt < num_k; ++kt, ++it) {
                 if ((it % GROUPS) != grp) continue;            // the other group's stage
@@ -296,50 +294,67 @@ panel_umma_kernel(const PanelParams p) {
                                                  SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles, 100);
                     __syncwarp();
                 }
+                // Publish the group's previous stage before filling this one.  Its copies were
+                // issued a whole iteration ago and have normally landed while the warp waited for
+                // the free slot, so this costs nothing -- whereas publishing after this stage's
+                // copies are issued (the load/store unit takes them at ~12 clk per warp copy)
+                // would hand the tensor core its data most of a microsecond late.
+                if (prev_s >= 0) {
+                    sm100::cp_async_wait<0>();
+                    sm100::fence_proxy_async_smem();   // every lane: its generic-proxy writes -> tensor-core reads
+                    __syncwarp();
+                    if (lane == 0) sm100::mbar_arrive(&full_bar[prev_s]);
+                }
                 if (pw == 0 && lane == 0) TRACE(0, it, 0);
-                prefetch_idx(pre, it + 2 * GROUPS);            // joins this iteration's cp.async group
-                for (int g = 0; g < GROUPS; ++g) advance(pre);
+                if (lane == 0) PTRACE(pidx, it, 0);
                 const int rows_valid = min(KS, ent.y - kt * KS);  // multiple of 16
                 const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
+                // Value panel slice [rows_valid][V]: stored in global memory in the byte order of
+                // the shared-memory operand tile, so one bulk copy by the copy engine places it;
+                // its bytes are added to what the stage's barrier waits for.
+                if (pw == 0 && lane == 0 && !(ablate & 4)) {
+                    const uint32_t wbytes = (uint32_t)(rows_valid * V * 2);
+                    sm100::mbar_expect_tx(&full_bar[s], wbytes);
+                    sm100::bulk_copy_g2s(st_base + (uint32_t)Cfg::G_BYTES, wsrc + (size_t)kt * KS * V, wbytes, &full_bar[s]);
+                }
+                prefetch_idx(pre, it + 2 * GROUPS);            // joins this iteration's cp.async group
+                for (int g = 0; g < GROUPS; ++g) advance(pre);
                 const int* ids = idx_ring + s_idx * KS;  // landed: their group was awaited last iteration
 
+                // All row ids / offsets are fetched into registers BEFORE the first copy: the copy
+                // instructions are ordered with respect to shared-memory reads, so a read placed
+                // between two copies would serialise its latency into every iteration.
                 if constexpr (!CONV) {
+                    int idr[NQ];
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) idr[q] = ids[rbase + q * RPI];
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) {
                         if (rbase + q * RPI < rows_valid && !(ablate & 2))
                             sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
-                                               lane_src0 + (size_t)ids[rbase + q * RPI] * row_pitch, nbytes);
+                                               lane_src0 + (uint64_t)(uint32_t)idr[q] * row_pitch, nbytes);
                     }
                 } else {
                     // Column ids arrive decoded (c | r << 16 | s << 24).  Lane j < RPW turns row
                     // pw*RPW + j into an element offset once; the copies fetch it by shuffle.
                     const int idv = ids[pw * RPW + (lane % RPW)];
                     const int delta = ((idv & 0xffff) * (p.Hp * p.Wp) + ((idv >> 16) & 0xff) * p.Wp + ((idv >> 24) & 0xff)) * p.Bp;
+                    int dq[NQ];
+#pragma unroll
+                    for (int q = 0; q < NQ; ++q) dq[q] = __shfl_sync(0xffffffffu, delta, q * RPI + sub);
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) {
-                        const int dq = __shfl_sync(0xffffffffu, delta, q * RPI + sub);
                         if (rbase + q * RPI < rows_valid && !(ablate & 2))
                             sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
-                                               conv_src0 + dq, nbytes);
+                                               conv_src0 + dq[q], nbytes);
                     }
-                }
-                // Value panel slice [rows_valid][V]: contiguous in global memory.
-#pragma unroll
-                for (int u = 0; u < WQ; ++u) {
-                    if (wrow[u] < rows_valid && !(ablate & 4))
-                        sm100::cp_async_16(st_base + woff[u], wsrc + (size_t)(kt * KS * V + u * GW * 32 * 8), 16u);
                 }
                 sm100::cp_async_commit();
                 if (pw == 0 && lane == 0) TRACE(0, it, 1);
-                // Publish the group's previous stage: this warp's copies for it have landed.
-                if (prev_s >= 0) {
-                    sm100::cp_async_wait<1>();
-                    sm100::fence_proxy_async_smem();   // every lane: its generic-proxy writes -> tensor-core reads
-                    __syncwarp();
-                    if (lane == 0) sm100::mbar_arrive(&full_bar[prev_s]);
-                }
+                if (lane == 0) PTRACE(pidx, it, 1);
                 prev_s = s;
                 if (pw == 0 && lane == 0) TRACE(0, it, 2);
+                if (lane == 0) PTRACE(pidx, it, 2);
             }
         }
         // Publish the group's last stage.
@@ -361,6 +376,9 @@ panel_umma_kernel(const PanelParams p) {
                     : sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 2048, sm100::kSwizzle128B);
         constexpr uint32_t WSTEP = V == 32 ? 1024 : V == 64 ? 2048 : 4096;  // bytes per K-step of the value tile
         int it = 0;
+#ifdef SHFLBW_ABLATE
+        long long c4_prev = 0;
+#endif
         bool next_ready = false;  // lane 0: the coming stage's barrier was already seen complete
         for (int li = 0; li < nloc; ++li) {
             const int rows_total = item_tab[li].y;
@@ -376,9 +394,16 @@ panel_umma_kernel(const PanelParams p) {
             for (int kt = 0; kt < num_k; ++kt, ++it) {
                 const int s = it % STAGES;
                 if (lane == 0) {
+#ifdef SHFLBW_ABLATE
+                    const long long cA = clock64();
+                    if (tracing && it < 256 && it > 0) { p.trace[8192 + 8 * 1024 + it * 4 + 1] = cA - c4_prev; p.trace[8192 + 8 * 1024 + it * 4 + 3] = next_ready; }
+#endif
                     if (!next_ready)
                         sm100::mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, cta_abort, p.status_word,
                                                  SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
+#ifdef SHFLBW_ABLATE
+                    if (tracing && it < 256) p.trace[8192 + 8 * 1024 + it * 4 + 2] = clock64() - cA;
+#endif
                     TRACE(1, it, 0);
 #ifdef SHFLBW_ABLATE
                     const long long c0 = clock64();
@@ -419,6 +444,10 @@ panel_umma_kernel(const PanelParams p) {
                     TRACE(1, it, 1);
                     // Test the next stage's barrier now: the round trip hides behind the MMAs just issued.
                     next_ready = sm100::mbar_test(&full_bar[(it + 1) % STAGES], ((it + 1) / STAGES) & 1);
+#ifdef SHFLBW_ABLATE
+                    c4_prev = clock64();
+                    if (tracing && it < 256) p.trace[8192 + 8 * 1024 + it * 4 + 0] = c4_prev - c3;
+#endif
                 }
                 __syncwarp();
             }
@@ -573,5 +602,6 @@ panel_umma_kernel(const PanelParams p) {
 
 #undef TRACE
 #undef CTRACE
+#undef PTRACE
 
 }  // namespace shflbw

@@ -152,7 +152,7 @@ void build_host_images(shflbw_matrix& m) {
         size_t r = (size_t)m.kptr[i];
         for (int p = b; p < e; ++p, ++r) {
             m.kidx[r] = m.indices[p];
-            std::memcpy(&m.kval[r * m.brow], &m.values[(size_t)p * m.brow], (size_t)m.brow * 2);
+            for (int j = 0; j < m.brow; ++j) m.kval[kval_index(m.brow, r, j)] = m.values[(size_t)p * m.brow + j];
         }
         for (; r < (size_t)m.kptr[i + 1]; ++r) m.kidx[r] = e > b ? m.indices[e - 1] : 0;
     }

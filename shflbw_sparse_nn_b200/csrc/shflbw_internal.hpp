@@ -13,6 +13,25 @@
 // kind::f16 consumes K = 16, so kernels never handle a ragged K tail.
 constexpr int kShflbwKPad = 16;
 
+// Kernel image of the value panels.  Element (padded row r, row-in-block m) lives at
+// kval_index(V, r, m).  For V = 32 / 64 / 128 every group of 8 rows is stored in exactly the
+// byte order the tensor-core operand tile has in shared memory (16-byte chunks XOR-swizzled by
+// the row, 128-byte or 64-byte swizzle atoms), so a pipeline stage of the panel is ONE
+// contiguous run that a bulk copy drops into place.  Other V: plain row-major.
+#if defined(__CUDACC__)
+#define SHFLBW_HD __host__ __device__
+#else
+#define SHFLBW_HD
+#endif
+SHFLBW_HD inline size_t kval_index(int V, size_t r, int m) {
+    const size_t r7 = r & 7, grp = (r >> 3) * 8 * (size_t)V;   // elements before this 8-row group
+    const int c = m >> 3, e = m & 7;                            // 16-byte chunk, element in chunk
+    if (V == 64) return grp + r7 * 64 + (size_t)((c ^ (int)r7) << 3) + e;
+    if (V == 128) return grp + (size_t)(c >> 3) * 512 + r7 * 64 + (size_t)(((c & 7) ^ (int)r7) << 3) + e;
+    if (V == 32) return grp + r7 * 32 + (size_t)((c ^ (int)((r7 >> 1) & 3)) << 3) + e;
+    return r * (size_t)V + m;
+}
+
 struct shflbw_matrix {
     // ---- logical format (same fields as BlockwiseSpMatrix / BlockwiseSpFilter) ----
     int nrow = 0, ncol = 0, nnzb = 0, brow = 0, bcol = 1;
@@ -29,7 +48,7 @@ struct shflbw_matrix {
     std::vector<int> meta_h;       // reference-compatible [indptr | indices*bcol | perm], pad 8
     std::vector<int> kptr, kidx;   // kernel image: padded offsets / column ids
     std::vector<int> kcrs;         // filters only: kidx decoded as c | r << 16 | s << 24 (k = (r*S + s)*C + c)
-    std::vector<uint16_t> kval;    // kernel image: padded fp16 panels [rows][brow]
+    std::vector<uint16_t> kval;    // kernel image: padded fp16 panels, element order kval_index()
 
     // ---- device copy (owned) ----
     int device = -1;

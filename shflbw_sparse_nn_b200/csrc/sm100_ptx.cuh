@@ -72,6 +72,18 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return mbar_wait_slow(bar, parity, cta_abort, status_word, code, limit_cycles, backoff_ns);
 }
 
+// ----------------------------------------------------------------- bulk copy ----
+// Adds `bytes` to the barrier's pending transaction count (no arrival).
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Contiguous global -> shared copy by the copy engine; completes `bytes` on the barrier.
+// Both addresses 16-byte aligned, bytes a multiple of 16.  The source is this GPU's memory.
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 // ------------------------------------------------------------------ cp.async ----
 // 16-byte global->shared copy through L2 only; src_bytes = 0 zero-fills the destination.
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {
