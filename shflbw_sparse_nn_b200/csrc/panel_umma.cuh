@@ -86,9 +86,9 @@ struct PanelCfg {
     static constexpr int W_BYTES = KS * V * 2;
     static constexpr int STAGE_BYTES = G_BYTES + W_BYTES;
     static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
-    // SpConv: each epilogue warp transposes 32 positions x 32 filters through 2 KB so that its
-    // global stores are 64-byte runs; the SpMM epilogue stores straight from registers.
-    static constexpr int OUT_BYTES = CONV ? 8 * 2048 : 0;
+    // Each epilogue warp transposes 32 tokens x 32 output rows / filters through 2 KB so that
+    // its global stores are 16 bytes per lane and 64-byte runs.
+    static constexpr int OUT_BYTES = 8 * 2048;
     static constexpr int BAR_BYTES = (STAGES * 2 + 8) * 8;   // mbarriers + tmem slot + abort flag
     static constexpr int TAB_BYTES = 512 * 8;               // per-CTA item table (kPanelMaxItemsPerCta entries)
     static constexpr int IDX_RING = 8;                      // stages of row ids kept in shared memory
@@ -488,7 +488,6 @@ panel_umma_kernel(const PanelParams p) {
             const int tok = reads ? n0 + a0 * 128 + quad * 32 + lane : p.N;   // idle warps store nothing
             const int mbase = col0 % V;                    // first block row / filter of this warp
             bool ok = tok < p.N && !(ablate & 8);
-            uint32_t my_off = 0;                           // SpMM: row offset of block row mbase + 32*g + lane
             uint32_t row_off[4];                           // SpConv: output offsets of positions i*8 + lane/4
             if constexpr (CONV) {
                 const int pix = tok / p.Bp, img = tok - pix * p.Bp;
@@ -502,43 +501,71 @@ panel_umma_kernel(const PanelParams p) {
             }
             const bool use_c = p.beta != 0.0f && p.C != nullptr;
             if constexpr (!CONV) {
-#pragma unroll 1   // a short loop body: the three roles share a small instruction cache
-            for (int c0 = 0; c0 < COLS; c0 += 8) {
-                uint32_t r[8];
-                if (has_k && reads) {
-                    sm100::tmem_ld_32x32b_x8(acc_base + c0, r);
-                    sm100::tmem_ld_wait();
-                } else {
+            // SpMM: thread = token, accumulator columns = the block's output rows.  For a fixed
+            // row a warp's 32 tokens are only 64 contiguous bytes of D, and storing them straight
+            // from registers is one 2-byte-per-lane store per row.  Instead each chunk of 32 rows
+            // goes through a [32 rows][32 tokens] tile in shared memory (2-byte writes, one row =
+            // 64 contiguous bytes, conflict-free) and comes back as 16-byte pieces: four lanes
+            // store one row's 64 bytes, eight rows per store instruction.  The inverse row
+            // permutation is the row index of those stores.
+            __half* my_tile = (__half*)(smem + Cfg::PIPE_BYTES + warp * 2048);
+            const int tg = lane & 3;                                    // 8-token group stored by this lane
+            const int tok_g = reads ? n0 + a0 * 128 + quad * 32 + tg * 8 : p.N;
+            const bool ok_g = tok_g < p.N && !(ablate & 8);             // N % 8 == 0: a group is valid as a whole
+#pragma unroll 1
+            for (int cc = 0; cc < COLS; cc += 32) {
+                uint32_t roff[4];                                        // D offsets of rows cc + 8i + lane/4
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) r[j] = 0u;
+                for (int i = 0; i < 4; ++i) {
+                    const int m = mbase + cc + 8 * i + (lane >> 2);
+                    const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
+                    roff[i] = (uint32_t)row * (uint32_t)p.N;
                 }
-                if (c0 + 8 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
-                    sm100::tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
-                    if (tid == 0) TRACE(2, li, 1);
-                }
-                if (ablate & 512) continue;
-                {
-                    // Thread = token, registers = 8 output rows of the block.  For a fixed row the
-                    // warp's 32 tokens are 64 contiguous bytes of D: one warp store per row straight
-                    // from registers; the inverse row permutation is the row index of that store.
-                    if ((c0 & 31) == 0) {  // lane j fetches the destination row of block row mbase+c0+j
-                        const int m = mbase + c0 + lane;
-                        const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + (m < V ? m : V - 1)) : blk * V + m;
-                        my_off = (uint32_t)row * (uint32_t)p.N;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c0 = cc + j * 8;
+                    uint32_t r[8];
+                    if (has_k && reads) {
+                        sm100::tmem_ld_32x32b_x8(acc_base + c0, r);
+                        sm100::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) r[e] = 0u;
                     }
+                    if (c0 + 8 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
+                        sm100::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
+                        if (tid == 0) TRACE(2, li, 1);
+                    }
+                    // Same epilogue arithmetic as the reference: round to fp16, then alpha (and
+                    // beta * C, applied after the transpose) in fp16.
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const uint32_t off = __shfl_sync(0xffffffffu, my_off, (c0 & 31) + j) + (uint32_t)tok;
-                        __half h = __float2half_rn(__uint_as_float(r[j]));
-                        if (ok) {
-                            if (use_c) h = __hfma(h, alpha1, __hmul(p.C[off], beta1));
-                            else h = __hmul(h, alpha1);
-                            p.D[off] = h;
+                    for (int e = 0; e < 8; ++e) {
+                        __half h = __float2half_rn(__uint_as_float(r[e]));
+                        if (!use_c) h = __hmul(h, alpha1);
+                        my_tile[(j * 8 + e) * 32 + lane] = h;
+                    }
+                }
+                __syncwarp();
+                if (!(ablate & 512)) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 v = *(const uint4*)(my_tile + (8 * i + (lane >> 2)) * 32 + tg * 8);
+                        if (ok_g) {
+                            const size_t off = (size_t)roff[i] + (size_t)tok_g;
+                            if (use_c) {
+                                const uint4 cv = *(const uint4*)(p.C + off);
+                                __half* h = (__half*)&v;
+                                const __half* ch = (const __half*)&cv;
+#pragma unroll
+                                for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
+                            }
+                            *(uint4*)(p.D + off) = v;
                         }
                     }
                 }
+                __syncwarp();
             }
             } else {
             // SpConv: thread = output position, accumulator columns = consecutive filters of the
