@@ -74,13 +74,12 @@ template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
 struct PanelCfg {
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
-    // Warp w runs on scheduler partition w % 4.  The MMA warp (8) sits on partition 0; with 8
-    // producer warps the block carries two idle warps (12, 16) so that no producer shares that
-    // partition -- the MMA warp executes a few dozen instructions per stage and was measured at
-    // ~20 clk per instruction when producer code kept evicting its lines from the partition's
-    // instruction cache.
-    static constexpr bool SPARE_P0 = PW == 8;
-    static constexpr int THREADS = SPARE_P0 ? 19 * 32 : (9 + PW) * 32;
+    // Warp w runs on scheduler partition w % 4.  The MMA warp (8) sits on partition 0 and no
+    // producer shares it: warps 12, 16, 20... of the block stay idle.  The MMA warp executes a
+    // few dozen instructions per stage and was measured at ~20 clk per instruction when
+    // producer code kept evicting its lines from the partition's instruction cache.
+    static constexpr int WARPS = 9 + PW + (PW - 1) / 3;     // 8 epilogue + MMA + producers + idle
+    static constexpr int THREADS = WARPS * 32;
     static constexpr int G_ACC = KS * 256;                 // gathered tile of one accumulator: [KS][128] fp16
     static constexpr int G_BYTES = TM * G_ACC;
     static constexpr int W_BYTES = KS * V * 2;
@@ -188,8 +187,8 @@ panel_umma_kernel(const PanelParams p) {
     if (tid == 0) TRACE(3, 0, 0);
     if (tid == 0) CTRACE(1);
 
-    const int pidx = Cfg::SPARE_P0 ? warp - 9 - (warp > 12) - (warp > 16) : warp - 9;   // producer number
-    if (Cfg::SPARE_P0 && (warp == 12 || warp == 16)) {
+    const int pidx = warp - 9 - (warp / 4 - 2);   // producer number of a producer warp (warps 9.. with warp % 4 != 0)
+    if (warp >= 9 && (warp & 3) == 0) {
         // idle: keeps producers off the MMA warp's scheduler partition
     } else if (warp >= 9) {
         // ------------------------------------------------------------- producers ----
@@ -294,21 +293,24 @@ panel_umma_kernel(const PanelParams p) {
                                                  SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles, 100);
                     __syncwarp();
                 }
-                // Publish the group's previous stage before filling this one.  Its copies were
-                // issued a whole iteration ago and have normally landed while the warp waited for
-                // the free slot, so this costs nothing -- whereas publishing after this stage's
-                // copies are issued (the load/store unit takes them at ~12 clk per warp copy)
-                // would hand the tensor core its data most of a microsecond late.
-                if (prev_s >= 0) {
-                    sm100::cp_async_wait<0>();
-                    sm100::fence_proxy_async_smem();   // every lane: its generic-proxy writes -> tensor-core reads
-                    __syncwarp();
-                    if (lane == 0) sm100::mbar_arrive(&full_bar[prev_s]);
-                }
                 if (pw == 0 && lane == 0) TRACE(0, it, 0);
                 if (lane == 0) PTRACE(pidx, it, 0);
                 const int rows_valid = min(KS, ent.y - kt * KS);  // multiple of 16
                 const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
+                // The group's previous stage is published half-way through this stage's copies:
+                // the first half is committed as its own cp.async group, and "all but the newest
+                // group" then covers every copy of the previous stage -- issued at least half an
+                // issue phase ago, so the wait does not stall, while the tensor core gets the
+                // stage half an issue phase earlier than if it were published at the end.
+                auto publish_prev = [&]() {
+                    sm100::cp_async_commit();
+                    if (prev_s >= 0) {
+                        sm100::cp_async_wait<1>();
+                        sm100::fence_proxy_async_smem();   // every lane: its generic-proxy writes -> tensor-core reads
+                        __syncwarp();
+                        if (lane == 0) sm100::mbar_arrive(&full_bar[prev_s]);
+                    }
+                };
                 // Value panel slice [rows_valid][V]: stored in global memory in the byte order of
                 // the shared-memory operand tile, so one bulk copy by the copy engine places it;
                 // its bytes are added to what the stage's barrier waits for.
@@ -330,6 +332,7 @@ panel_umma_kernel(const PanelParams p) {
                     for (int q = 0; q < NQ; ++q) idr[q] = ids[rbase + q * RPI];
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) {
+                        if (q == NQ / 2) publish_prev();
                         if (rbase + q * RPI < rows_valid && !(ablate & 2))
                             sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
                                                lane_src0 + (uint64_t)(uint32_t)idr[q] * row_pitch, nbytes);
@@ -344,6 +347,7 @@ panel_umma_kernel(const PanelParams p) {
                     for (int q = 0; q < NQ; ++q) dq[q] = __shfl_sync(0xffffffffu, delta, q * RPI + sub);
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) {
+                        if (q == NQ / 2) publish_prev();
                         if (rbase + q * RPI < rows_valid && !(ablate & 2))
                             sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
                                                conv_src0 + dq[q], nbytes);
@@ -375,53 +379,32 @@ panel_umma_kernel(const PanelParams p) {
           : V == 64 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 1024, sm100::kSwizzle128B)
                     : sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 2048, sm100::kSwizzle128B);
         constexpr uint32_t WSTEP = V == 32 ? 1024 : V == 64 ? 2048 : 4096;  // bytes per K-step of the value tile
-        int it = 0;
-#ifdef SHFLBW_ABLATE
-        long long c4_prev = 0;
-#endif
-        bool next_ready = false;  // lane 0: the coming stage's barrier was already seen complete
-        for (int li = 0; li < nloc; ++li) {
-            const int rows_total = item_tab[li].y;
-            const int num_k = (rows_total + KS - 1) / KS;
-            const int b = li & 1;
-            if (li >= 2) {
-                if (lane == 0)
+        // One thread runs the whole role (tcgen05.mma / commit are single-thread instructions):
+        // no per-stage warp synchronisation, and the ring slot and its parity are carried
+        // instead of being recomputed by division.
+        if (lane == 0) {
+            int it = 0;
+            uint32_t s = 0, ph = 0;     // ring slot of stage `it` and the parity of its full barrier
+            bool ready = false;         // that barrier was already seen complete
+            for (int li = 0; li < nloc; ++li) {
+                const int rows_total = item_tab[li].y;
+                const int num_k = (rows_total + KS - 1) / KS;
+                const int b = li & 1;
+                if (li >= 2)
                     sm100::mbar_wait_bounded(&acc_empty[b], ((li >> 1) - 1) & 1, cta_abort, p.status_word,
                                              SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 20);
-                __syncwarp();
-            }
-            const uint32_t acc_base = tmem_base + b * Cfg::ACC_COLS;
-            for (int kt = 0; kt < num_k; ++kt, ++it) {
-                const int s = it % STAGES;
-                if (lane == 0) {
-#ifdef SHFLBW_ABLATE
-                    const long long cA = clock64();
-                    if (tracing && it < 256 && it > 0) { p.trace[8192 + 8 * 1024 + it * 4 + 1] = cA - c4_prev; p.trace[8192 + 8 * 1024 + it * 4 + 3] = next_ready; }
-#endif
-                    if (!next_ready)
-                        sm100::mbar_wait_bounded(&full_bar[s], (it / STAGES) & 1, cta_abort, p.status_word,
+                const uint32_t acc_base = tmem_base + b * Cfg::ACC_COLS;
+                for (int kt = 0; kt < num_k; ++kt, ++it) {
+                    if (!ready)
+                        sm100::mbar_wait_bounded(&full_bar[s], ph, cta_abort, p.status_word,
                                                  SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
-#ifdef SHFLBW_ABLATE
-                    if (tracing && it < 256) p.trace[8192 + 8 * 1024 + it * 4 + 2] = clock64() - cA;
-#endif
                     TRACE(1, it, 0);
-#ifdef SHFLBW_ABLATE
-                    const long long c0 = clock64();
-#endif
                     if (!(ablate & 16)) sm100::fence_proxy_async_smem();  // cp.async (generic proxy) data -> tensor-core (async proxy) reads
-#ifdef SHFLBW_ABLATE
-                    const long long c1 = clock64();
-#endif
                     sm100::tc_fence_after_sync();
-#ifdef SHFLBW_ABLATE
-                    const long long c1b = clock64();
-                    if (tracing && it < 256) p.trace[3 * 1024 + it * 4 + 0] = c1b - c1;
-#endif
                     const int nk = (ablate & 1) ? 0 : min(KS, rows_total - kt * KS) / 16;
-                    const uint64_t gd = gdesc0 + (uint64_t)((uint32_t)(s * Cfg::STAGE_BYTES) >> 4);
-                    const uint64_t wd = wdesc0 + (uint64_t)((uint32_t)(s * Cfg::STAGE_BYTES) >> 4);
                     // compact loop (not unrolled): the three roles share a small instruction cache
-                    uint64_t gdj = gd, wdj = wd;
+                    uint64_t gdj = gdesc0 + (uint64_t)((s * (uint32_t)Cfg::STAGE_BYTES) >> 4);
+                    uint64_t wdj = wdesc0 + (uint64_t)((s * (uint32_t)Cfg::STAGE_BYTES) >> 4);
                     uint32_t accum = (uint32_t)(kt != 0);
 #pragma unroll 1
                     for (int j = 0; j < nk; ++j) {
@@ -432,31 +415,18 @@ panel_umma_kernel(const PanelParams p) {
                         wdj += WSTEP >> 4;
                         accum = 1u;
                     }
-#ifdef SHFLBW_ABLATE
-                    const long long c2 = clock64();
-#endif
                     if (ablate & 64) sm100::mbar_arrive(&empty_bar[s]);
                     else sm100::umma_commit(&empty_bar[s]);  // stage may be refilled once these MMAs retire
-#ifdef SHFLBW_ABLATE
-                    const long long c3 = clock64();
-                    if (tracing && it < 256) { p.trace[3 * 1024 + it * 4 + 1] = c1 - c0; p.trace[3 * 1024 + it * 4 + 2] = c2 - c1; p.trace[3 * 1024 + it * 4 + 3] = c3 - c2; }
-#endif
                     TRACE(1, it, 1);
                     // Test the next stage's barrier now: the round trip hides behind the MMAs just issued.
-                    next_ready = sm100::mbar_test(&full_bar[(it + 1) % STAGES], ((it + 1) / STAGES) & 1);
-#ifdef SHFLBW_ABLATE
-                    c4_prev = clock64();
-                    if (tracing && it < 256) p.trace[8192 + 8 * 1024 + it * 4 + 0] = c4_prev - c3;
-#endif
+                    if (++s == (uint32_t)STAGES) { s = 0; ph ^= 1u; }
+                    ready = sm100::mbar_test(&full_bar[s], ph);
                 }
-                __syncwarp();
-            }
-            if (lane == 0) {
                 if (num_k > 0 && !(ablate & 1)) sm100::umma_commit(&acc_full[b]);  // accumulator complete
                 else sm100::mbar_arrive(&acc_full[b]);                             // nothing to wait for
             }
-            __syncwarp();
         }
+        __syncwarp();
         if (lane == 0) CTRACE(3);
     } else {
         // -------------------------------------------------------------- epilogue ----
