@@ -13,19 +13,19 @@
 // gathered from L2.
 //
 // One CTA per SM loops over items (item = blockIdx.x + i*gridDim.x); their extents are read
-// once into a shared-memory table.  Warp roles:
-//   warps 0-7        epilogue: TMEM -> registers -> fp16 -> global (inverse row permutation
-//                    fused); warp w reads TMEM lane quadrant w % 4, column half w / 4
-//   warp  8          allocates TMEM, issues tcgen05.mma (lane 0), releases stages and
+// once into a shared-memory table.  Warp roles (warp w issues from scheduler partition w % 4):
+//   warps 0-7        epilogue: TMEM -> registers -> fp16 -> 32x32 transpose in shared memory ->
+//                    16-byte global stores (inverse row permutation fused for SpMM); warp w
+//                    reads TMEM lane quadrant w % 4, column half w / 4
+//   warp  8          allocates TMEM; its lane 0 issues tcgen05.mma, releases stages and
 //                    accumulators with tcgen05.commit
-//   warps 9..9+PW-1  producers: 16-byte cp.async gathers into 128-byte-swizzled stages.
-//                    A warp runs LAG stages ahead of its own copies (cp.async groups) and
-//                    publishes a stage with ONE mbarrier arrival per warp; the ring has more
-//                    stages than LAG+1 so the MMA warp is not in lock-step with the producers.
-//                    Row ids are prefetched 3 stages ahead in registers.
-//                    The measured L2->SM gather rate on B200 grows with the number of
-//                    issuing warps (4 warps/SM: 5 TB/s, 16 warps/SM: 16 TB/s), hence many
-//                    producer warps.
+//   warps 9.. with w % 4 != 0   producers (PW of them, in two groups that take the stages in
+//                    turn): 16-byte cp.async gathers into 128-byte-swizzled stages, one bulk
+//                    copy per stage for the value slice.  A group publishes its previous stage
+//                    half-way through issuing the next one, with ONE mbarrier arrival per warp.
+//                    Row ids are prefetched two of the group's stages ahead by 4-byte cp.async
+//                    into a shared-memory ring.
+//   warps 12, 16     idle, so that no producer shares the MMA warp's scheduler partition.
 // The accumulator is double buffered in TMEM so the epilogue of item i overlaps the main
 // loop of item i+1, and the stage ring runs across item boundaries without draining.
 //
@@ -70,7 +70,7 @@ struct PanelParams {
     int Bn, Bp, Hp, Wp, Cin, F, R, S, stride, Ho, Wo;
 };
 
-template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
+template <int V, int TM, int KS_, int STAGES, int PW, bool CONV>
 struct PanelCfg {
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
@@ -99,7 +99,6 @@ struct PanelCfg {
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte swizzle-atom alignment");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
     static_assert(KS % 16 == 0 && KS % PW == 0 && (KS / PW) % (32 / (T / 8)) == 0, "rows per producer warp");
-    static_assert(LAG_ >= 1 && LAG_ < STAGES && LAG_ + 2 <= IDX_RING, "a warp may run at most STAGES-1 stages ahead of its own copies");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -119,10 +118,10 @@ __device__ __forceinline__ uint32_t tile32_off(int r, int c) { return (uint32_t)
 
 constexpr int kPanelMaxItemsPerCta = 512;  // capacity of the per-CTA item table
 
-template <int V, int TM, int KS_, int STAGES, int LAG_, int PW, bool CONV>
-__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, LAG_, PW, CONV>::THREADS, 1)
+template <int V, int TM, int KS_, int STAGES, int PW, bool CONV>
+__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, CONV>::THREADS, 1)
 panel_umma_kernel(const PanelParams p) {
-    using Cfg = PanelCfg<V, TM, KS_, STAGES, LAG_, PW, CONV>;
+    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, CONV>;
     constexpr int KS = Cfg::KS, T = Cfg::T;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: swizzle atoms are addressed by absolute shared-memory address bits.

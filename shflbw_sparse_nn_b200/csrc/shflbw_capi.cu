@@ -41,34 +41,27 @@ int ensure_buffer(void** buf, size_t* have, size_t need) {
 using PanelKernel = void (*)(const shflbw::PanelParams);
 struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; };
 
-template <int V, int TM, int KS, int STAGES, int LAG, int PW, bool CONV>
+template <int V, int TM, int KS, int STAGES, int PW, bool CONV>
 PanelChoice choice() {
-    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, LAG, PW, CONV>;
-    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, LAG, PW, CONV>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
+    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, CONV>;
+    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, CONV>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
             Cfg::THREADS};
 }
 
-// Pipeline shape per (V, tile): non-zero columns per stage (KS), ring depth (as many stages
-// as fit in ~200 KB of shared memory) and LAG, the number of stages a producer warp keeps in
-// flight before it publishes the oldest.  variant 0 is the default; others are tuning aids
-// selected with SHFLBW_VARIANT.
-template <bool CONV, int PW>
-bool lookup(int V, int tile, int variant, PanelChoice* out) {
-    switch ((V * 1000 + tile) * 10 + variant) {
-        case 321280:  *out = choice<32, 1, 64, 8, 4, PW, CONV>(); return true;    // 20 KB stages
-        case 322560:  *out = choice<32, 2, 64, 5, 2, PW, CONV>(); return true;    // 36 KB
-        case 641280:  *out = choice<64, 1, 64, 8, 4, PW, CONV>(); return true;    // 24 KB
-        case 642560:  *out = choice<64, 2, 64, 5, 2, PW, CONV>(); return true;    // 40 KB
-        case 642561:  *out = choice<64, 2, 64, 5, 3, PW, CONV>(); return true;
-        case 1281280: *out = choice<128, 1, 64, 6, 3, PW, CONV>(); return true;   // 32 KB
-        case 1282560: *out = choice<128, 2, 64, 4, 2, PW, CONV>(); return true;   // 48 KB
+// Pipeline shape per (V, tile): non-zero columns per stage (KS) and ring depth (as many stages
+// as fit beside the 16 KB of epilogue tiles).  Eight producer warps: 12 and 16 were measured
+// and bring nothing.
+template <bool CONV>
+bool lookup(int V, int tile, PanelChoice* out) {
+    switch (V * 1000 + tile) {
+        case 32128:  *out = choice<32, 1, 64, 8, 8, CONV>(); return true;    // 20 KB stages
+        case 32256:  *out = choice<32, 2, 64, 5, 8, CONV>(); return true;    // 36 KB
+        case 64128:  *out = choice<64, 1, 64, 8, 8, CONV>(); return true;    // 24 KB
+        case 64256:  *out = choice<64, 2, 64, 5, 8, CONV>(); return true;    // 40 KB
+        case 128128: *out = choice<128, 1, 64, 6, 8, CONV>(); return true;   // 32 KB
+        case 128256: *out = choice<128, 2, 64, 4, 8, CONV>(); return true;   // 48 KB
         default: return false;
     }
-}
-
-template <bool CONV>
-bool lookup_pw(int V, int tile, int pw, int variant, PanelChoice* out) {
-    return pw == 16 ? lookup<CONV, 16>(V, tile, variant, out) : lookup<CONV, 8>(V, tile, variant, out);
 }
 
 // Persistent launch: one CTA per SM, more only when a CTA's share would overflow its item table.
@@ -87,25 +80,21 @@ int sm_count() {
 
 // Tile selection.  A 256-token work item halves the value-panel traffic per token and is
 // the default; 128 is used when the dense extent is too small to give every SM a few items.
-// SHFLBW_TILE=128|256 and SHFLBW_PW=8|16 override (tuning aids).
+// SHFLBW_TILE=128|256 overrides (tuning aid).
 template <bool CONV>
 int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
     // Token tile: a persistent CTA works through ceil(items / SMs) items in turn; an item of
-    // the 128-token tile was measured at ~0.6x the time of a 256-token item (half the
+    // the 128-token tile was measured at ~2/3 of the time of a 256-token item (half the
     // gathered bytes, the same number of pipeline stages).
-    int tile = 256, pw = 8;
+    int tile = 256;
     const int sms = sm_count() > 0 ? sm_count() : 148;
     const long long items256 = ((n_tokens + 255) / 256) * row_blocks;
     const long long items128 = ((n_tokens + 127) / 128) * row_blocks;
     const long long waves256 = (items256 + sms - 1) / sms, waves128 = (items128 + sms - 1) / sms;
-    if (n_tokens <= 128 || waves128 * 6 < waves256 * 10) tile = 128;
+    if (n_tokens <= 128 || waves128 * 2 < waves256 * 3) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
-    if (const char* e = getenv("SHFLBW_PW")) { int t = atoi(e); if (t == 8 || t == 16) pw = t; }
-    int variant = 0;
-    if (const char* e = getenv("SHFLBW_VARIANT")) variant = atoi(e);
-    if (!lookup_pw<CONV>(V, tile, pw, variant, out) && !lookup_pw<CONV>(V, tile, pw, variant = 0, out))
-        return SHFLBW_ERR_UNSUPPORTED;
-    out->variant = variant;
+    if (!lookup<CONV>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
+    out->variant = 0;
     CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
     return SHFLBW_OK;
 }
@@ -248,7 +237,7 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         // The state is a POD and may have been copied: re-derive the function pointer from the
         // recorded configuration (the shared-memory attribute was set at init).
         PanelChoice ch;
-        if (!lookup_pw<false>(st->V, st->tokens_per_cta, st->producer_warps, st->variant, &ch)) return SHFLBW_ERR_INVALID_ARG;
+        if (!lookup<false>(st->V, st->tokens_per_cta, &ch)) return SHFLBW_ERR_INVALID_ARG;
         shflbw::PanelParams p{};
         p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
@@ -369,7 +358,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
         return SHFLBW_OK;
     }
     PanelChoice ch;
-    if (!lookup_pw<true>(st->V, st->tokens_per_cta, st->producer_warps, st->variant, &ch)) return SHFLBW_ERR_INVALID_ARG;
+    if (!lookup<true>(st->V, st->tokens_per_cta, &ch)) return SHFLBW_ERR_INVALID_ARG;
     // 1. NHWC -> channel-major, batch-innermost staging with a zero halo.
     const int Hp = st->Hin + st->R - 1, Wp = st->Win + st->S - 1;
     {
