@@ -61,5 +61,34 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+TOOLS_DIR = PKG_DIR / "bin"
+TOOL_SOURCE = PKG_DIR / "csrc" / "benchmark_cli.cu"
+
+
+def build_tools(force: bool = False) -> dict:
+    """Compile the command-line benchmarks (`bin/benchmark.spmm.out`, `bin/benchmark.spconv.out`):
+    same flags and output line as the reference's tools of those names.  They link the library
+    through an rpath relative to their own location."""
+    build_library()
+    TOOLS_DIR.mkdir(exist_ok=True)
+    out = {}
+    for name, defs in (("benchmark.spmm.out", []), ("benchmark.spconv.out", ["-DSHFLBW_BENCH_SPCONV"])):
+        exe = TOOLS_DIR / name
+        out[name] = exe
+        deps = [TOOL_SOURCE, REPO_ROOT / "include" / "shflbw.h", REPO_ROOT / "include" / "shflbw_compat.hpp"]
+        if not force and exe.exists() and all(d.stat().st_mtime <= exe.stat().st_mtime for d in deps):
+            continue
+        cmd = [_nvcc(), "-ccbin", "g++", "-O2", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a",
+               "-I", str(REPO_ROOT / "include"), *defs, str(TOOL_SOURCE), "-L", str(PKG_DIR), "-lshflbw_b200",
+               "-Xlinker", "-rpath=$ORIGIN/..", "-o", str(exe)]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+    return out
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--tools" in sys.argv:
+        for exe in build_tools(force="--force" in sys.argv).values():
+            print(exe)
