@@ -217,6 +217,10 @@ typedef struct shflbw_spconv_state {
     const void* blk_val;
     const int* perm;
     int* status_word;
+    /* chained layers (shflbw_spconv_chain_init): ifmap / ofmap are chain buffers, no scratch */
+    int chain;               /* 1: input and output are chain buffers                   */
+    int out_R, out_S;        /* filter shape of the consumer the output halo is for     */
+    int relu;                /* 1: max(x, 0) fused into the epilogue                    */
 } shflbw_spconv_state_t;
 
 /* Replaces SpconvBlockwiseOp::initialize / SpconvBlockwiseInitFn
@@ -234,6 +238,41 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream);
 /* End-to-end conv with HOST NHWC buffers. */
 int shflbw_spconv_host(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
                        const void* ifmap_host, void* ofmap_host, float alpha);
+
+/* ---- Chained SpConv layers.  No counterpart in the reference project (its epilogue hooks,
+ * block_sparse/common/epilogue.h:6-135, and the "online transformation" of docs/format.pdf are
+ * the pointers).  Between two Shfl-BW conv layers the activation does not have to go back to
+ * NHWC in logical channel order: a CHAIN BUFFER holds it as fp16 [C][H+R-1][W+S-1][Bp] --
+ * channel-major, batch innermost and rounded up to 8 (Bp), with a zero halo sized for the R x S
+ * filter of the layer that will READ it (image origin at (R/2, S/2)), and with channels in the
+ * STORED filter order of the layer that wrote it.  A chained layer is then one kernel launch:
+ * no relayout before it and no inverse permutation after it.
+ *
+ *   x NHWC --import--> buf0 --conv1--> buf1 --conv2--> buf2 --export--> y NHWC
+ *
+ * The caller owns the buffers (shflbw_chain_buffer_elems fp16 elements each) and zero-fills
+ * each ONCE before first use: layers write only the interior, the halo has to stay zero.
+ * conv2's filter must address its input channels in conv1's stored order: build it with
+ * shflbw_filter_fold_input_order(filter2, filter1).  Results equal the unchained path up to
+ * fp32 summation order (folding re-sorts the columns of a row block). */
+size_t shflbw_chain_buffer_elems(int C, int H, int W, int B, int R_consumer, int S_consumer);
+/* NHWC (logical channel order) -> chain buffer for a consumer with an R x S filter. */
+int shflbw_chain_import_nhwc(const void* nhwc, int B, int H, int W, int C, int R_consumer, int S_consumer,
+                             void* chain_buf, void* stream);
+/* Chain buffer written by `producer` (halo for R x S) -> NHWC in logical channel order
+ * (producer's inverse filter permutation applied; producer == NULL: channels as stored). */
+int shflbw_chain_export_nhwc(const void* chain_buf, int B, int H, int W, int F, int R_halo, int S_halo,
+                             const shflbw_matrix_t* producer, void* nhwc, void* stream);
+/* New filter = `filter` with its input channels renumbered to the stored filter order of
+ * `producer` (filter->C == producer->F); column lists re-sorted, values moved with them. */
+int shflbw_filter_fold_input_order(const shflbw_matrix_t* filter, const shflbw_matrix_t* producer,
+                                   shflbw_matrix_t** out);
+/* One chained layer: in_chain has the halo of THIS filter, out_chain the halo of the consumer's
+ * R_next x S_next filter (1 x 1 for none).  relu != 0 fuses max(x, 0).  Run with shflbw_spconv_exec
+ * (one launch, no scratch, no allocation). */
+int shflbw_spconv_chain_init(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
+                             const void* in_chain, void* out_chain, int R_next, int S_next,
+                             float alpha, int relu, shflbw_spconv_state_t* out);
 
 /* SpConv for callers that must not allocate.  No counterpart in the reference project.
  *

@@ -6,7 +6,8 @@ operator interface over that library's C ABI (include/shflbw.h).
 """
 from ._cabi import (KERNEL_AUTO, KERNEL_SIMT, KERNEL_TCGEN05, VALUES_INT9_LIBC, VALUES_UNIFORM,
                     ShflbwError)
-from .blockwise import (BlockwiseSpFilter, BlockwiseSpMatrix, SpconvBlockwiseExecFn,
+from .blockwise import (BlockwiseSpFilter, BlockwiseSpMatrix, SpconvBlockwiseExecFn, SpconvChainOp,
+                        chain_buffer_elems, chain_export_nhwc, chain_import_nhwc,
                         SpconvBlockwiseInitFn, SpconvBlockwiseOp, SpmmBlockwiseExecFn,
                         SpmmBlockwiseInitFn, SpmmBlockwiseOp, spconv_host, spmm_host, uniform_half)
 
@@ -14,5 +15,6 @@ __all__ = [
     "BlockwiseSpMatrix", "BlockwiseSpFilter", "SpmmBlockwiseOp", "SpmmBlockwiseInitFn",
     "SpmmBlockwiseExecFn", "SpconvBlockwiseOp", "SpconvBlockwiseInitFn", "SpconvBlockwiseExecFn",
     "spmm_host", "spconv_host", "uniform_half", "ShflbwError",
+    "SpconvChainOp", "chain_buffer_elems", "chain_import_nhwc", "chain_export_nhwc",
     "KERNEL_AUTO", "KERNEL_TCGEN05", "KERNEL_SIMT", "VALUES_INT9_LIBC", "VALUES_UNIFORM",
 ]

@@ -54,6 +54,7 @@ class SpconvState(C.Structure):
         ("staged_out", C.c_void_p), ("staged_in_bytes", C.c_size_t), ("staged_out_bytes", C.c_size_t),
         ("blk_ptr", C.c_void_p), ("blk_idx", C.c_void_p), ("blk_val", C.c_void_p),
         ("perm", C.c_void_p), ("status_word", C.c_void_p),
+        ("chain", C.c_int), ("out_R", C.c_int), ("out_S", C.c_int), ("relu", C.c_int),
     ]
 
 
@@ -101,6 +102,12 @@ _PROTOS = {
     "shflbw_spconv_exec": (C.c_int, [C.POINTER(SpconvState), C.c_void_p]),
     "shflbw_spconv_host": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_float]),
     "shflbw_spconv_launches_per_exec": (C.c_int, [C.POINTER(SpconvState)]),
+    "shflbw_chain_buffer_elems": (C.c_size_t, [C.c_int] * 6),
+    "shflbw_chain_import_nhwc": (C.c_int, [C.c_void_p] + [C.c_int] * 6 + [C.c_void_p, C.c_void_p]),
+    "shflbw_chain_export_nhwc": (C.c_int, [C.c_void_p] + [C.c_int] * 6 + [_H, C.c_void_p, C.c_void_p]),
+    "shflbw_filter_fold_input_order": (C.c_int, [_H, _H, C.POINTER(_H)]),
+    "shflbw_spconv_chain_init": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                           C.c_int, C.c_int, C.c_float, C.c_int, C.POINTER(SpconvState)]),
     "shflbw_spconv_exec_static_scratch": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                     C.c_float, C.c_void_p]),
 }

@@ -199,6 +199,14 @@ class BlockwiseSpFilter(BlockwiseSpMatrix):
         check(_cabi.lib().shflbw_matrix_filter_shape(self._h, *[C.byref(x) for x in v]), "filter_shape")
         return tuple(x.value for x in v)
 
+    def fold_input_order(self, producer: "BlockwiseSpMatrix") -> "BlockwiseSpFilter":
+        """This filter with its input channels renumbered to `producer`'s stored filter order
+        (for chained layers: the producer's output is consumed without its inverse permutation)."""
+        out = BlockwiseSpFilter()
+        check(_cabi.lib().shflbw_filter_fold_input_order(self._h, producer._h, C.byref(out._h)), "fold_input_order")
+        out.initialized = True
+        return out
+
     F = property(lambda s: s._shape()[0])
     R = property(lambda s: s._shape()[1])
     S = property(lambda s: s._shape()[2])
@@ -276,6 +284,52 @@ class SpconvBlockwiseOp:
 
     def __call__(self, stream=None):
         check(_cabi.lib().shflbw_spconv_exec(C.byref(self._state), _stream_ptr(stream)), "SpconvBlockwiseOp()")
+
+    @property
+    def launches_per_exec(self) -> int:
+        return _cabi.lib().shflbw_spconv_launches_per_exec(C.byref(self._state))
+
+    @property
+    def out_hw(self):
+        return self._state.Ho, self._state.Wo
+
+
+# Chained conv layers: activations stay in the channel-major, halo-padded "chain buffer"
+# layout between layers (see include/shflbw.h).  No counterpart in the reference.
+
+def chain_buffer_elems(C_, H, W, B, R_consumer=1, S_consumer=1) -> int:
+    return int(_cabi.lib().shflbw_chain_buffer_elems(C_, H, W, B, R_consumer, S_consumer))
+
+
+def chain_import_nhwc(x_nhwc, B, H, W, C_, R_consumer, S_consumer, chain_buf, stream=None) -> None:
+    check(_cabi.lib().shflbw_chain_import_nhwc(_ptr(x_nhwc), B, H, W, C_, R_consumer, S_consumer, _ptr(chain_buf),
+                                               _stream_ptr(stream)), "chain_import_nhwc")
+
+
+def chain_export_nhwc(chain_buf, B, H, W, F, R_halo, S_halo, producer, y_nhwc, stream=None) -> None:
+    check(_cabi.lib().shflbw_chain_export_nhwc(_ptr(chain_buf), B, H, W, F, R_halo, S_halo,
+                                               producer._h if producer is not None else None, _ptr(y_nhwc),
+                                               _stream_ptr(stream)), "chain_export_nhwc")
+
+
+class SpconvChainOp:
+    """One chained layer: chain buffer in (halo of this filter), chain buffer out (halo of the
+    consumer's R_next x S_next filter), optional fused ReLU; one kernel launch."""
+
+    def __init__(self):
+        self._state = SpconvState()
+        self._keep = None
+
+    def initialize(self, spfilter: BlockwiseSpFilter, B, H, W, stride, in_chain, out_chain, R_next=1, S_next=1,
+                   alpha: float = 1.0, relu: bool = False):
+        check(_cabi.lib().shflbw_spconv_chain_init(spfilter._h, B, H, W, stride, _ptr(in_chain), _ptr(out_chain),
+                                                   R_next, S_next, float(alpha), int(bool(relu)),
+                                                   C.byref(self._state)), "SpconvChainOp.initialize")
+        self._keep = (spfilter, in_chain, out_chain)
+        return self
+
+    def __call__(self, stream=None):
+        check(_cabi.lib().shflbw_spconv_exec(C.byref(self._state), _stream_ptr(stream)), "SpconvChainOp()")
 
     @property
     def launches_per_exec(self) -> int:

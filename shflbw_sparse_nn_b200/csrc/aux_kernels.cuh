@@ -107,6 +107,36 @@ unpermute_filters(const __half* __restrict__ staged, __half* __restrict__ out, c
     }
 }
 
+// Chain buffer -> NHWC: out[n][h][w][perm[f]] = buf[f][h + ph][w + pw][n] (perm == nullptr:
+// channels stay in stored order).  One block: one pixel x 8 images x all F filters; reads are
+// 16 bytes (8 images of one (filter, pixel)), the F-vectors of the 8 images are assembled in
+// shared memory with 2-byte stores and leave as 16-byte stores.  Dynamic shared memory:
+// 8 * F * 2 bytes.  F % 8 == 0, Bp % 8 == 0.
+__global__ void __launch_bounds__(256)
+chain_export_nhwc(const __half* __restrict__ buf, __half* __restrict__ out, const int* __restrict__ perm,
+                  int Bn, int Bp, int H, int W, int Hp, int Wp, int ph, int pw, int F) {
+    extern __shared__ __align__(16) uint8_t export_smem[];
+    __half* vec = (__half*)export_smem;                  // [8 images][F]
+    const int groups = Bp / 8;
+    const int pix = blockIdx.x / groups, n0 = (blockIdx.x % groups) * 8;
+    const int h = pix / W, w = pix - h * W;
+    const size_t plane = (size_t)Hp * Wp * Bp;
+    const __half* src = buf + ((size_t)(h + ph) * Wp + (w + pw)) * Bp + n0;
+    for (int f = threadIdx.x; f < F; f += 256) {
+        const uint4 v = *(const uint4*)(src + (size_t)f * plane);
+        const __half* hv = (const __half*)&v;
+        const int c = perm ? __ldg(perm + f) : f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) vec[j * F + c] = hv[j];
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < F; e += 256) {         // e = (image j, 8-channel chunk)
+        const int j = e / (F / 8), c8 = (e - j * (F / 8)) * 8;
+        if (n0 + j < Bn)
+            *(uint4*)(out + (((size_t)(n0 + j) * H + h) * W + w) * F + c8) = *(const uint4*)(vec + j * F + c8);
+    }
+}
+
 // Plain SpMM: one thread per (stored row, dense column).
 __global__ void simt_spmm(const int* __restrict__ blk_ptr, const int* __restrict__ blk_idx,
                           const __half* __restrict__ blk_val, const int* __restrict__ perm,

@@ -68,9 +68,15 @@ struct PanelParams {
     const __half* Xs;
     __half* out;             // [B*Ho*Wo][F] (NHWC) -- final or staged in stored filter order
     int Bn, Bp, Hp, Wp, Cin, F, R, S, stride, Ho, Wo;
+    // chained SpConv: out[f][OHp][OWp][Bp] with the next layer's halo (origin at (oph, opw))
+    int OWp, oph, opw, out_plane, relu;
 };
 
-template <int V, int TM, int KS_, int STAGES, int PW, bool CONV>
+// MODE: 0 = SpMM, 1 = SpConv writing NHWC (stored filter order), 2 = SpConv writing the
+// channel-major halo layout the next layer gathers from ("chained" layers).
+constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2;
+
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE>
 struct PanelCfg {
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
@@ -118,10 +124,12 @@ __device__ __forceinline__ uint32_t tile32_off(int r, int c) { return (uint32_t)
 
 constexpr int kPanelMaxItemsPerCta = 512;  // capacity of the per-CTA item table
 
-template <int V, int TM, int KS_, int STAGES, int PW, bool CONV>
-__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, CONV>::THREADS, 1)
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE>
+__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE>::THREADS, 1)
 panel_umma_kernel(const PanelParams p) {
-    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, CONV>;
+    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE>;
+    constexpr bool CONV = MODE != kPanelSpmm;          // implicit-GEMM gather
+    constexpr bool ROWS_OUT = MODE != kPanelConv;      // output rows = block rows / filters, tokens contiguous
     constexpr int KS = Cfg::KS, T = Cfg::T;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: swizzle atoms are addressed by absolute shared-memory address bits.
@@ -458,7 +466,7 @@ panel_umma_kernel(const PanelParams p) {
             const int mbase = col0 % V;                    // first block row / filter of this warp
             bool ok = tok < p.N && !(ablate & 8);
             uint32_t row_off[4];                           // SpConv: output offsets of positions i*8 + lane/4
-            if constexpr (CONV) {
+            if constexpr (MODE == kPanelConv) {
                 const int pix = tok / p.Bp, img = tok - pix * p.Bp;
                 ok = ok && img < p.Bn;
                 const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
@@ -468,8 +476,8 @@ panel_umma_kernel(const PanelParams p) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) row_off[i] = __shfl_sync(0xffffffffu, mine, i * 8 + (lane >> 2));
             }
-            const bool use_c = p.beta != 0.0f && p.C != nullptr;
-            if constexpr (!CONV) {
+            const bool use_c = MODE == kPanelSpmm && p.beta != 0.0f && p.C != nullptr;
+            if constexpr (ROWS_OUT) {
             // SpMM: thread = token, accumulator columns = the block's output rows.  For a fixed
             // row a warp's 32 tokens are only 64 contiguous bytes of D, and storing them straight
             // from registers is one 2-byte-per-lane store per row.  Instead each chunk of 32 rows
@@ -481,14 +489,31 @@ panel_umma_kernel(const PanelParams p) {
             const int tg = lane & 3;                                    // 8-token group stored by this lane
             const int tok_g = reads ? n0 + a0 * 128 + quad * 32 + tg * 8 : p.N;
             const bool ok_g = tok_g < p.N && !(ablate & 8);             // N % 8 == 0: a group is valid as a whole
+            // Element offset of the group inside an output row.  SpMM: the token index.  Chained
+            // SpConv: 8 images of one output pixel inside the next layer's halo-padded plane
+            // (images beyond the batch are computed from zero inputs and are written as zeros).
+            uint32_t goff = (uint32_t)tok_g;
+            __half* const obase = MODE == kPanelSpmm ? p.D : p.out;
+            if constexpr (MODE == kPanelConvChain) {
+                if (ok_g) {
+                    const int pix = tok_g / p.Bp, nn = tok_g - pix * p.Bp;
+                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                    goff = (uint32_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
+                }
+            }
+            const __half zero1 = __float2half_rn(0.f);
 #pragma unroll 1
             for (int cc = 0; cc < COLS; cc += 32) {
                 uint32_t roff[4];                                        // D offsets of rows cc + 8i + lane/4
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int m = mbase + cc + 8 * i + (lane >> 2);
-                    const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
-                    roff[i] = (uint32_t)row * (uint32_t)p.N;
+                    if constexpr (MODE == kPanelSpmm) {
+                        const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
+                        roff[i] = (uint32_t)row * (uint32_t)p.N;
+                    } else {
+                        roff[i] = (uint32_t)(blk * V + m) * (uint32_t)p.out_plane;   // stored filter order
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -513,6 +538,7 @@ panel_umma_kernel(const PanelParams p) {
                     for (int e = 0; e < 8; ++e) {
                         __half h = __float2half_rn(__uint_as_float(r[e]));
                         if (!use_c) h = __hmul(h, alpha1);
+                        if (MODE == kPanelConvChain && p.relu) h = __hmax(h, zero1);
                         my_tile[(j * 8 + e) * 32 + lane] = h;
                     }
                 }
@@ -522,7 +548,7 @@ panel_umma_kernel(const PanelParams p) {
                     for (int i = 0; i < 4; ++i) {
                         uint4 v = *(const uint4*)(my_tile + (8 * i + (lane >> 2)) * 32 + tg * 8);
                         if (ok_g) {
-                            const size_t off = (size_t)roff[i] + (size_t)tok_g;
+                            const size_t off = (size_t)roff[i] + (size_t)goff;
                             if (use_c) {
                                 const uint4 cv = *(const uint4*)(p.C + off);
                                 __half* h = (__half*)&v;
@@ -530,7 +556,7 @@ panel_umma_kernel(const PanelParams p) {
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
                             }
-                            *(uint4*)(p.D + off) = v;
+                            *(uint4*)(obase + off) = v;
                         }
                     }
                 }

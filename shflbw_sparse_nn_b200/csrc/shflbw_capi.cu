@@ -41,25 +41,25 @@ int ensure_buffer(void** buf, size_t* have, size_t need) {
 using PanelKernel = void (*)(const shflbw::PanelParams);
 struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; };
 
-template <int V, int TM, int KS, int STAGES, int PW, bool CONV>
+template <int V, int TM, int KS, int STAGES, int PW, int MODE>
 PanelChoice choice() {
-    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, CONV>;
-    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, CONV>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
+    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, MODE>;
+    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, MODE>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
             Cfg::THREADS};
 }
 
 // Pipeline shape per (V, tile): non-zero columns per stage (KS) and ring depth (as many stages
 // as fit beside the 16 KB of epilogue tiles).  Eight producer warps: 12 and 16 were measured
 // and bring nothing.
-template <bool CONV>
+template <int MODE>
 bool lookup(int V, int tile, PanelChoice* out) {
     switch (V * 1000 + tile) {
-        case 32128:  *out = choice<32, 1, 64, 8, 8, CONV>(); return true;    // 20 KB stages
-        case 32256:  *out = choice<32, 2, 64, 5, 8, CONV>(); return true;    // 36 KB
-        case 64128:  *out = choice<64, 1, 64, 8, 8, CONV>(); return true;    // 24 KB
-        case 64256:  *out = choice<64, 2, 64, 5, 8, CONV>(); return true;    // 40 KB
-        case 128128: *out = choice<128, 1, 64, 6, 8, CONV>(); return true;   // 32 KB
-        case 128256: *out = choice<128, 2, 64, 4, 8, CONV>(); return true;   // 48 KB
+        case 32128:  *out = choice<32, 1, 64, 8, 8, MODE>(); return true;    // 20 KB stages
+        case 32256:  *out = choice<32, 2, 64, 5, 8, MODE>(); return true;    // 36 KB
+        case 64128:  *out = choice<64, 1, 64, 8, 8, MODE>(); return true;    // 24 KB
+        case 64256:  *out = choice<64, 2, 64, 5, 8, MODE>(); return true;    // 40 KB
+        case 128128: *out = choice<128, 1, 64, 6, 8, MODE>(); return true;   // 32 KB
+        case 128256: *out = choice<128, 2, 64, 4, 8, MODE>(); return true;   // 48 KB
         default: return false;
     }
 }
@@ -81,7 +81,7 @@ int sm_count() {
 // Tile selection.  A 256-token work item halves the value-panel traffic per token and is
 // the default; 128 is used when the dense extent is too small to give every SM a few items.
 // SHFLBW_TILE=128|256 overrides (tuning aid).
-template <bool CONV>
+template <int MODE>
 int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
     // Token tile: a persistent CTA works through ceil(items / SMs) items in turn; an item of
     // the 128-token tile was measured at ~2/3 of the time of a 256-token item (half the
@@ -93,7 +93,7 @@ int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
     const long long waves256 = (items256 + sms - 1) / sms, waves128 = (items128 + sms - 1) / sms;
     if (n_tokens <= 128 || waves128 * 2 < waves256 * 3) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
-    if (!lookup<CONV>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
+    if (!lookup<MODE>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
     out->variant = 0;
     CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
     return SHFLBW_OK;
@@ -210,7 +210,7 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
         out->tokens_per_cta = 128; out->stages = 0; out->shared_mem_size = 0;
     } else {
         PanelChoice ch;
-        int rc = pick_panel<false>(m->brow, N, out->num_row_blocks, &ch);
+        int rc = pick_panel<shflbw::kPanelSpmm>(m->brow, N, out->num_row_blocks, &ch);
         if (rc != SHFLBW_OK) return rc;
         out->kernel = SHFLBW_KERNEL_TCGEN05;
         out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
@@ -237,7 +237,7 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         // The state is a POD and may have been copied: re-derive the function pointer from the
         // recorded configuration (the shared-memory attribute was set at init).
         PanelChoice ch;
-        if (!lookup<false>(st->V, st->tokens_per_cta, &ch)) return SHFLBW_ERR_INVALID_ARG;
+        if (!lookup<shflbw::kPanelSpmm>(st->V, st->tokens_per_cta, &ch)) return SHFLBW_ERR_INVALID_ARG;
         shflbw::PanelParams p{};
         p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
@@ -279,6 +279,16 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
 
 // ---------------------------------------------------------------------------- SpConv --
 
+// NHWC -> [C][Hin+R-1][Win+S-1][Bp] with a zero halo (origin at (R/2, S/2)).
+static void launch_relayout(const __half* in, __half* staged, int B, int Bp, int Hin, int Win, int C, int R, int S,
+                            cudaStream_t s) {
+    const int Hp = Hin + R - 1, Wp = Win + S - 1, PP = Hp * Wp;
+    const int NT = Bp < 32 ? Bp : 32, PT = shflbw::kRelayoutSlots / NT;
+    const int n_tiles = (Bp + NT - 1) / NT;
+    dim3 grid((unsigned)(((PP + PT - 1) / PT) * n_tiles), (unsigned)((C + shflbw::kRelayoutC - 1) / shflbw::kRelayoutC));
+    shflbw::relayout_nhwc_to_chwn<<<grid, 256, 0, s>>>(in, staged, B, Bp, Hin, Win, Hp, Wp, R / 2, S / 2, C);
+}
+
 // Dynamic shared memory of unpermute_filters: 16-bit permutation + one F-vector of fp16 per warp.
 static size_t unperm_smem_bytes(int F) { return (size_t)F * 2 * (1 + shflbw::kUnpermWarps); }
 
@@ -318,7 +328,7 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
         return SHFLBW_OK;
     }
     PanelChoice ch;
-    int rc = pick_panel<true>(f->brow, tokens, f->F / f->brow, &ch);
+    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, &ch);
     if (rc != SHFLBW_OK) return rc;
     out->kernel = SHFLBW_KERNEL_TCGEN05;
     out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
@@ -358,24 +368,27 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
         return SHFLBW_OK;
     }
     PanelChoice ch;
-    if (!lookup<true>(st->V, st->tokens_per_cta, &ch)) return SHFLBW_ERR_INVALID_ARG;
-    // 1. NHWC -> channel-major, batch-innermost staging with a zero halo.
+    const bool ok_kernel = st->chain ? lookup<shflbw::kPanelConvChain>(st->V, st->tokens_per_cta, &ch)
+                                     : lookup<shflbw::kPanelConv>(st->V, st->tokens_per_cta, &ch);
+    if (!ok_kernel) return SHFLBW_ERR_INVALID_ARG;
+    // 1. NHWC -> channel-major, batch-innermost staging with a zero halo (chained layers get
+    //    their input in that layout already).
     const int Hp = st->Hin + st->R - 1, Wp = st->Win + st->S - 1;
-    {
-        const int PP = Hp * Wp;
-        const int NT = st->Bp < 32 ? st->Bp : 32, PT = shflbw::kRelayoutSlots / NT;
-        const int n_tiles = (st->Bp + NT - 1) / NT;
-        dim3 grid((unsigned)(((PP + PT - 1) / PT) * n_tiles), (unsigned)((st->C + shflbw::kRelayoutC - 1) / shflbw::kRelayoutC));
-        shflbw::relayout_nhwc_to_chwn<<<grid, 256, 0, s>>>((const __half*)st->ifmap, (__half*)st->staged_in, st->B,
-                                                           st->Bp, st->Hin, st->Win, Hp, Wp, st->R / 2, st->S / 2, st->C);
-    }
+    if (!st->chain)
+        launch_relayout((const __half*)st->ifmap, (__half*)st->staged_in, st->B, st->Bp, st->Hin, st->Win, st->C,
+                        st->R, st->S, s);
     // 2. implicit-GEMM panel kernel.
     shflbw::PanelParams p{};
     p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
     p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = 0.f;
     p.N = st->Ho * st->Wo * st->Bp;
-    p.Xs = (const __half*)st->staged_in;
+    p.Xs = (const __half*)(st->chain ? st->ifmap : st->staged_in);
     p.out = (__half*)(st->staged_out ? st->staged_out : st->ofmap);
+    if (st->chain) {
+        const int OHp = st->Ho + st->out_R - 1;
+        p.OWp = st->Wo + st->out_S - 1; p.oph = st->out_R / 2; p.opw = st->out_S / 2;
+        p.out_plane = OHp * p.OWp * st->Bp; p.relu = st->relu;
+    }
     p.Bn = st->B; p.Bp = st->Bp; p.Hp = Hp; p.Wp = Wp; p.Cin = st->C; p.F = st->F;
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
     p.num_items = st->num_items; p.tiles_n = st->tiles_n;
@@ -398,7 +411,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
 
 int shflbw_spconv_launches_per_exec(const shflbw_spconv_state_t* st) {
     if (!st || !st->init_success) return 0;
-    if (st->kernel == SHFLBW_KERNEL_SIMT) return 1;
+    if (st->kernel == SHFLBW_KERNEL_SIMT || st->chain) return 1;
     return st->staged_out ? 3 : 2;
 }
 
@@ -423,6 +436,87 @@ int shflbw_spconv_host(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
 }
 
 // SpConv without any allocation: scratch lives in g_static_scratch (see shflbw.h).
+// ---- chained layers ---------------------------------------------------------------------
+
+size_t shflbw_chain_buffer_elems(int C, int H, int W, int B, int R, int S) {
+    if (C <= 0 || H <= 0 || W <= 0 || B <= 0 || R <= 0 || S <= 0) return 0;
+    return (size_t)C * (H + R - 1) * (W + S - 1) * ((B + 7) / 8 * 8);
+}
+
+int shflbw_chain_import_nhwc(const void* nhwc, int B, int H, int W, int C, int R, int S, void* chain_buf,
+                             void* stream) {
+    if (!nhwc || !chain_buf || B <= 0 || H <= 0 || W <= 0 || C <= 0 || R <= 0 || S <= 0) return SHFLBW_ERR_INVALID_ARG;
+    if (C % 8 || (((uintptr_t)nhwc | (uintptr_t)chain_buf) & 15)) return SHFLBW_ERR_UNSUPPORTED;
+    if ((long long)shflbw_chain_buffer_elems(C, H, W, B, R, S) >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+    launch_relayout((const __half*)nhwc, (__half*)chain_buf, B, (B + 7) / 8 * 8, H, W, C, R, S, (cudaStream_t)stream);
+    CK(cudaGetLastError());
+    return SHFLBW_OK;
+}
+
+int shflbw_chain_export_nhwc(const void* chain_buf, int B, int H, int W, int F, int R, int S,
+                             const shflbw_matrix_t* producer, void* nhwc, void* stream) {
+    if (!chain_buf || !nhwc || B <= 0 || H <= 0 || W <= 0 || F <= 0 || R <= 0 || S <= 0) return SHFLBW_ERR_INVALID_ARG;
+    if (F % 8 || (((uintptr_t)nhwc | (uintptr_t)chain_buf) & 15)) return SHFLBW_ERR_UNSUPPORTED;
+    const int* perm = nullptr;
+    if (producer) {
+        if (producer->nrow != F) return SHFLBW_ERR_BAD_FORMAT;
+        if (!producer->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+        perm = producer->d_perm;
+    }
+    const size_t smem = (size_t)F * 16;
+    if (smem > 227 * 1024) return SHFLBW_ERR_UNSUPPORTED;
+    if (smem > 48 * 1024)
+        CK(cudaFuncSetAttribute((const void*)shflbw::chain_export_nhwc, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int Bp = (B + 7) / 8 * 8;
+    const long long blocks = (long long)H * W * (Bp / 8);
+    if (blocks >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+    shflbw::chain_export_nhwc<<<(unsigned)blocks, 256, smem, (cudaStream_t)stream>>>(
+        (const __half*)chain_buf, (__half*)nhwc, perm, B, Bp, H, W, H + R - 1, W + S - 1, R / 2, S / 2, F);
+    CK(cudaGetLastError());
+    return SHFLBW_OK;
+}
+
+int shflbw_spconv_chain_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* in_chain,
+                             void* out_chain, int R_next, int S_next, float alpha, int relu,
+                             shflbw_spconv_state_t* out) {
+    if (!out) return SHFLBW_ERR_INVALID_ARG;
+    std::memset(out, 0, sizeof *out);
+    if (!f || !in_chain || !out_chain || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0 || R_next <= 0 || S_next <= 0)
+        return SHFLBW_ERR_INVALID_ARG;
+    if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
+    if (!f->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+    if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    if (f->C % 8 || !f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
+    if (((uintptr_t)in_chain | (uintptr_t)out_chain) & 15) return SHFLBW_ERR_UNSUPPORTED;
+    const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
+    const int Bp = (B + 7) / 8 * 8;
+    const long long tokens = (long long)Ho * Wo * Bp;
+    // 32-bit element offsets into both chain buffers
+    if (tokens >= (1ll << 31) || (long long)shflbw_chain_buffer_elems(f->C, Hin, Win, B, f->R, f->S) >= (1ll << 31) ||
+        (long long)shflbw_chain_buffer_elems(f->F, Ho, Wo, B, R_next, S_next) >= (1ll << 32) - 1)
+        return SHFLBW_ERR_UNSUPPORTED;
+    out->B = B; out->Hin = Hin; out->Win = Win; out->C = f->C; out->F = f->F; out->R = f->R; out->S = f->S;
+    out->stride = stride; out->Ho = Ho; out->Wo = Wo; out->V = f->brow; out->Bp = Bp;
+    out->alpha = alpha; out->ifmap = in_chain; out->ofmap = out_chain;
+    out->blk_ptr = f->d_kptr; out->blk_idx = f->d_kcrs; out->blk_val = f->d_val;
+    out->perm = f->d_perm; out->status_word = f->d_status;
+    out->chain = 1; out->out_R = R_next; out->out_S = S_next; out->relu = relu != 0;
+    PanelChoice ch;
+    int rc = pick_panel<shflbw::kPanelConvChain>(f->brow, tokens, f->F / f->brow, &ch);
+    if (rc != SHFLBW_OK) return rc;
+    out->kernel = SHFLBW_KERNEL_TCGEN05;
+    out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
+    out->tiles_n = (int)((tokens + ch.tokens - 1) / ch.tokens);
+    out->num_items = out->tiles_n * (f->F / f->brow);
+    const int sms = sm_count();
+    if (sms <= 0) return SHFLBW_ERR_CUDA;
+    out->block_x = ch.threads;
+    out->grid_x = persistent_grid(out->num_items, sms); out->grid_y = 1;
+    out->shared_mem_size = ch.smem;
+    out->init_success = 1;
+    return SHFLBW_OK;
+}
+
 int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, int Win, int stride,
                                       const void* ifmap, void* ofmap, float alpha, void* stream) {
     if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
@@ -464,7 +558,7 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     shflbw_spconv_state_t st;
     std::memset(&st, 0, sizeof st);
     PanelChoice ch;
-    int rc = pick_panel<true>(f->brow, tokens, f->F / f->brow, &ch);
+    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, &ch);
     if (rc != SHFLBW_OK) return rc;
     const int sms = sm_count();
     if (sms <= 0) return SHFLBW_ERR_CUDA;

@@ -340,6 +340,42 @@ int shflbw_matrix_create_from_arrays(int nrow, int ncol, int brow, int nnzb, con
     return SHFLBW_OK;
 }
 
+int shflbw_filter_fold_input_order(const shflbw_matrix_t* f, const shflbw_matrix_t* producer,
+                                   shflbw_matrix_t** out) {
+    if (!out) return SHFLBW_ERR_INVALID_ARG;
+    *out = nullptr;
+    if (!f || !producer || !f->is_filter) return SHFLBW_ERR_INVALID_ARG;
+    if (f->C != producer->nrow) return SHFLBW_ERR_BAD_FORMAT;
+    // stored position of every logical channel of the producer's output
+    std::vector<int> where(f->C);
+    for (int p = 0; p < f->C; ++p) where[producer->row_permute ? producer->row_permute_ids[p] : p] = p;
+    // Column k = (r*S + s)*C + c keeps its tap and gets channel where[c]; every row block's
+    // list is sorted again (the format's invariant) and the value panels follow their columns.
+    std::vector<int> indices(f->indices.size());
+    std::vector<uint16_t> values(f->values.size());
+    std::vector<std::pair<int, int>> order;
+    const int X = f->nrow / f->brow;
+    for (int i = 0; i < X; ++i) {
+        const int b = f->indptr[i], e = f->indptr[i + 1];
+        order.clear();
+        for (int p = b; p < e; ++p) {
+            const int k = f->indices[p];
+            order.emplace_back((k / f->C) * f->C + where[k % f->C], p);
+        }
+        std::sort(order.begin(), order.end());
+        for (int j = 0; j < e - b; ++j) {
+            indices[b + j] = order[j].first;
+            std::memcpy(&values[(size_t)(b + j) * f->brow], &f->values[(size_t)order[j].second * f->brow],
+                        (size_t)f->brow * 2);
+        }
+    }
+    int rc = shflbw_matrix_create_from_arrays(f->nrow, f->ncol, f->brow, f->nnzb, f->indptr.data(), indices.data(),
+                                              values.data(), f->row_permute ? f->row_permute_ids.data() : nullptr, out);
+    if (rc != SHFLBW_OK) return rc;
+    (*out)->seed = f->seed;
+    return shflbw_matrix_set_filter_shape(*out, f->F, f->R, f->S, f->C);
+}
+
 int shflbw_matrix_load_text(const char* text, size_t len, shflbw_matrix_t** out) {
     if (!text || !out) return SHFLBW_ERR_INVALID_ARG;
     *out = nullptr;

@@ -116,3 +116,35 @@ def test_empty_and_ragged_row_blocks():
     assert m.nnzb == 18 and list(np.diff(m.indptr)) == [0, 1, 17]
     meta = m.meta_h
     assert meta.size == 8 + 24 + 0 and np.array_equal(meta[:4], indptr) and np.array_equal(meta[8:26], indices)
+
+
+def test_fold_input_order_relabels_channels_and_keeps_the_format_invariants():
+    """shflbw_filter_fold_input_order: column (r, s, c) moves to (r, s, stored position of c in the
+    producer); lists stay sorted, values follow their columns, the filter's own permutation stays."""
+    prod = sb.BlockwiseSpFilter().init_random(64, 1, 1, 16, 32, 1, 0.5, True, 3, values="uniform")
+    f = sb.BlockwiseSpFilter().init_random(96, 3, 3, 64, 32, 1, 0.2, True, 4, values="uniform")
+    g = f.fold_input_order(prod)
+    g.validate()
+    assert (g.F, g.R, g.S, g.C, g.nnzb, g.brow) == (f.F, f.R, f.S, f.C, f.nnzb, f.brow)
+    assert np.array_equal(g.indptr, f.indptr) and np.array_equal(g.row_permute_ids, f.row_permute_ids)
+
+    def dense(m):
+        d = np.zeros((m.nrow, m.ncol), np.uint16)
+        v = m.values.reshape(-1, m.brow)
+        for i in range(m.nrow // m.brow):
+            for p in range(m.indptr[i], m.indptr[i + 1]):
+                d[i * m.brow:(i + 1) * m.brow, m.indices[p]] = v[p]
+        return d
+
+    where = np.empty(64, np.int64)
+    where[prod.row_permute_ids] = np.arange(64)          # logical channel -> stored position
+    cols = (np.arange(f.ncol) // 64) * 64 + where[np.arange(f.ncol) % 64]
+    want = np.zeros_like(dense(f))
+    want[:, cols] = dense(f)
+    assert np.array_equal(dense(g), want)
+    for i in range(g.nrow // g.brow):
+        assert np.all(np.diff(g.indices[g.indptr[i]:g.indptr[i + 1]]) > 0)
+    # a producer without a permutation folds to the identity
+    ident = sb.BlockwiseSpFilter().init_random(64, 1, 1, 16, 32, 1, 0.5, False, 3, values="uniform")
+    h = f.fold_input_order(ident)
+    assert np.array_equal(h.indices, f.indices) and np.array_equal(h.values, f.values)
