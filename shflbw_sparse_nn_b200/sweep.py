@@ -3,7 +3,7 @@
 benchmark.spmm.out / benchmark.spconv.out over lists of shapes.
 
     python -m shflbw_sparse_nn_b200.sweep spmm      [--reps 50] [--json out.json]
-    python -m shflbw_sparse_nn_b200.sweep resnet50  [--batch 256] [--reps 20] [--json out.json]
+    python -m shflbw_sparse_nn_b200.sweep resnet50  [--batch 256] [--reps 20] [--chained] [--json out.json]
 
 `spmm` walks transformer projection shapes x N x V x density with seeded masks and uniform
 values and prints, per shape, the time, nonzero and dense-equivalent TFLOP/s and the fraction
@@ -12,6 +12,8 @@ the HBM peak).  `resnet50` times every pruned 1x1 / 3x3 layer shape of the ResNe
 (V=64, density 0.2) at the given batch and reports images/s over the pruned layers of one
 forward pass (each distinct shape weighted by how often the [3,4,6,3] stack uses it; the dense
 7x7 stem and the pooling / classifier layers are not part of the sparse path and not timed).
+With --chained every layer runs as a chained layer (activations stay channel-major, halo-padded
+and in stored filter order between layers; one launch per layer, ReLU fused).
 
 Timing follows the reference's tool (benchmark/benchmark.spmm.cu:36-49): warm-up launches,
 then the mean over `reps` launches between two CUDA events.  Inputs alternate between buffers
@@ -106,7 +108,21 @@ def sweep_resnet50(args, sb, torch):
         nb = max(2, min(4, -(-L2_BYTES // per) + 1))
         xs = [(torch.rand((Bn, Hin, Win, Cc), generator=gen, device="cuda") * 2 - 1).half() for _ in range(nb)]
         os_ = [torch.empty((Bn, Ho, Wo, F), dtype=torch.float16, device="cuda") for _ in range(nb)]
-        ops = [sb.SpconvBlockwiseOp().initialize(f, Bn, Hin, Win, stride, xs[i], os_[i]) for i in range(nb)]
+        if args.chained:
+            # activations stay in the chain-buffer layout: one launch per layer, ReLU fused,
+            # output halo sized for a 3x3 consumer (the larger of the two cases in this stack)
+            del xs, os_
+            ins = [torch.zeros(sb.chain_buffer_elems(Cc, Hin, Win, Bn, R, S), dtype=torch.float16, device="cuda")
+                   for _ in range(nb)]
+            for b_ in ins:
+                b_.view(Cc, -1)[:, :].uniform_(-1, 1, generator=gen)   # halo values do not affect the timing
+            xs = ins
+            os_ = [torch.zeros(sb.chain_buffer_elems(F, Ho, Wo, Bn, 3, 3), dtype=torch.float16, device="cuda")
+                   for _ in range(nb)]
+            ops = [sb.SpconvChainOp().initialize(f, Bn, Hin, Win, stride, xs[i], os_[i], 3, 3, relu=True)
+                   for i in range(nb)]
+        else:
+            ops = [sb.SpconvBlockwiseOp().initialize(f, Bn, Hin, Win, stride, xs[i], os_[i]) for i in range(nb)]
         t = _time(torch, ops, args.reps)
         f.device_status()
         flops = 2.0 * f.nnzb * 64 * Bn * Ho * Wo
@@ -119,8 +135,8 @@ def sweep_resnet50(args, sb, torch):
         print("conv {Ho:3d}x{Wo:<3d} C={C:5d} F={F:5d} {R}x{S}/{stride} x{uses}: {us:9.1f} us  {nonzero_tflops:7.1f} nz-TFLOP/s  "
               "roofline {roofline_frac:.3f}  tile {tile}".format(**row), flush=True)
         del ops, xs, os_, f
-    summary = dict(batch=Bn, pruned_layers_ms=total * 1e3, images_per_s=Bn / total)
-    print("resnet50 pruned layers, batch {batch}: {pruned_layers_ms:.3f} ms per forward pass -> {images_per_s:.0f} images/s".format(**summary))
+    summary = dict(batch=Bn, chained=bool(args.chained), pruned_layers_ms=total * 1e3, images_per_s=Bn / total)
+    print("resnet50 pruned layers, batch {batch}, chained={chained}: {pruned_layers_ms:.3f} ms per forward pass -> {images_per_s:.0f} images/s".format(**summary))
     return rows + [summary]
 
 
@@ -130,6 +146,8 @@ def main(argv=None):
     ap.add_argument("--reps", type=int, default=30)
     ap.add_argument("--batch", type=int, default=256)
     ap.add_argument("--max-n", type=int, default=0, help="spmm: skip dense widths above this")
+    ap.add_argument("--chained", action="store_true",
+                    help="resnet50: time every layer as a chained layer (chain buffers in and out, one launch)")
     ap.add_argument("--hbm-gbs", type=float, default=6460.5)
     ap.add_argument("--tflops", type=float, default=1632.1)
     ap.add_argument("--json", default="")
