@@ -297,7 +297,7 @@ panel_umma_kernel(const PanelParams p) {
                 if (it >= STAGES) {  // one lane polls; the warp follows through __syncwarp
                     if (lane == 0)
                         sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
-                                                 SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles, 100);
+                                                 SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles, 32);
                     __syncwarp();
                 }
                 if (pw == 0 && lane == 0) TRACE(0, it, 0);
@@ -453,7 +453,7 @@ panel_umma_kernel(const PanelParams p) {
             const int b = li & 1;
             if (lane == 0)
                 sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
-                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 200);
+                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 32);
             __syncwarp();
             sm100::tc_fence_after_sync();
             if (tid == 0) TRACE(2, li, 0);
@@ -515,18 +515,16 @@ panel_umma_kernel(const PanelParams p) {
                         roff[i] = (uint32_t)(blk * V + m) * (uint32_t)p.out_plane;   // stored filter order
                     }
                 }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int c0 = cc + j * 8;
-                    uint32_t r[8];
+                {
+                    uint32_t r[32];                       // the chunk's 32 accumulator columns of this token
                     if (has_k && reads) {
-                        sm100::tmem_ld_32x32b_x8(acc_base + c0, r);
+                        sm100::tmem_ld_32x32b_x32(acc_base + cc, r);
                         sm100::tmem_ld_wait();
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) r[e] = 0u;
+                        for (int e = 0; e < 32; ++e) r[e] = 0u;
                     }
-                    if (c0 + 8 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
+                    if (cc + 32 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
                         sm100::tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
@@ -535,11 +533,11 @@ panel_umma_kernel(const PanelParams p) {
                     // Same epilogue arithmetic as the reference: round to fp16, then alpha (and
                     // beta * C, applied after the transpose) in fp16.
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
+                    for (int e = 0; e < 32; ++e) {
                         __half h = __float2half_rn(__uint_as_float(r[e]));
                         if (!use_c) h = __hmul(h, alpha1);
                         if (MODE == kPanelConvChain && p.relu) h = __hmax(h, zero1);
-                        my_tile[(j * 8 + e) * 32 + lane] = h;
+                        my_tile[e * 32 + lane] = h;
                     }
                 }
                 __syncwarp();

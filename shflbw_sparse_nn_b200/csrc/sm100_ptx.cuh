@@ -68,7 +68,11 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
                                                   int* status_word, int code, long long limit_cycles,
                                                   uint32_t backoff_ns = 40) {
-    if (mbar_test(bar, parity)) return true;
+    // Most waits in the kernels are short (a few hundred clocks): poll a handful of times in
+    // line before paying for the call and the first sleep of the slow path.
+#pragma unroll 1
+    for (int i = 0; i < 12; ++i)
+        if (mbar_test(bar, parity)) return true;
     return mbar_wait_slow(bar, parity, cta_abort, status_word, code, limit_cycles, backoff_ns);
 }
 
