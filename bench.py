@@ -49,9 +49,9 @@ METRIC = "spmm_nonzero_tflops"
 UNIT = "TFLOP/s"
 
 # DRAM bytes (read + write) of one SpMM kernel launch on the workload above, from the ncu
-# capture summarised in profiles/panel_umma_spmm_4096_v64.md (37.1 MB read + 4.1 MB written;
+# capture summarised in profiles/panel_umma_spmm_4096_v64.md (37.1 MB read + 3.8 MB written;
 # the D tile stays in L2 past the end of the launch).
-NCU_DRAM_BYTES_PER_LAUNCH = 41_267_328
+NCU_DRAM_BYTES_PER_LAUNCH = 40_938_880
 
 
 def peaks():
@@ -113,6 +113,27 @@ class ClockSampler:
         reasons = sorted({n for r in use for n, v in zip(names, r[3]) if v.lower().startswith("active")})
         return {"sm_mhz": statistics.median(r[1] for r in use), "sm_max_mhz": use[0][2], "reasons": reasons,
                 "samples": len(use), "window": window}
+
+
+def capture_steps(torch, launch, steps, stream, use_graph=True):
+    """Capture G consecutive steps (G = largest divisor of `steps` up to 200) into a CUDA graph.
+    Returns (run, G): run() executes exactly `steps` steps on `stream`; G == 0 means plain launches.
+    launch(i, raw_stream) enqueues step i."""
+    G = max((g for g in range(1, min(steps, 200) + 1) if steps % g == 0), default=0) if use_graph else 0
+    if G < 2:
+        return (lambda: [launch(i, stream.cuda_stream) for i in range(steps)]), 0
+    side = torch.cuda.Stream()
+    side.wait_stream(stream)
+    with torch.cuda.stream(side):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            cap = torch.cuda.current_stream().cuda_stream
+            for i in range(G):
+                launch(i, cap)
+    torch.cuda.synchronize()
+    graph.replay()                          # one untimed replay (graph upload)
+    torch.cuda.synchronize()
+    return (lambda: [graph.replay() for _ in range(steps // G)]), G
 
 
 def build_problem(sb):
@@ -177,14 +198,18 @@ def run_ours(args):
     for i in range(W):
         step(i)
     torch.cuda.synchronize()
+
+    # The timed loop is launch-gap sensitive (a ~41 us kernel per step): consecutive steps are
+    # captured once into a CUDA graph and the graph is replayed.
+    run_steps, G = capture_steps(torch, lambda i, raw: ops[i % NB]._call_raw(raw), args.steps, stream,
+                                 use_graph=not args.no_graph)
     if dist:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall0 = time.time()
     e0.record(stream)
-    for i in range(args.steps):
-        step(i)
+    run_steps()
     e1.record(stream)
     torch.cuda.synchronize()
     t_wall1 = time.time()
@@ -220,14 +245,15 @@ def run_ours(args):
         "dtype": "f16", "data": "synthetic",
         "config": {"workload": "SpMM M=N=K=4096 V=64 density=0.1 row-permute seed=2021 fp16 uniform[-1,1)",
                    "nnzb": nnzb, "batches_rotated": NB, "l2": "inputs larger than L2 (4 x 67 MB rotated)",
-                   "per_gpu": "one 4096-column batch per step on every GPU; sparse operand replicated"},
+                   "per_gpu": "one 4096-column batch per step on every GPU; sparse operand replicated",
+                   "launch": (f"CUDA graph of {G} steps replayed {args.steps // G}x" if G else "one host launch per step")},
         "dense_equivalent_tflops": round(world * flops_dense / (ms_step * 1e-3) / 1e12, 2),
         "roofline": roofline, "gpu_launches": args.steps * ops[0].launches_per_exec, "clocks": clocks,
     }
 
     if args.quick:
         if rank == 0 and world == 1:
-            out["spconv"] = bench_spconv(sb, torch, pk, steps=30, warmup=5)
+            out["spconv"] = bench_spconv(sb, torch, pk, steps=30, warmup=5, use_graph=not args.no_graph)
         if dist:
             dist.barrier()
             dist.destroy_process_group()
@@ -258,7 +284,7 @@ def run_ours(args):
                   "call": "shflbw_spmm_host (pinned host B and D)"}
 
     if rank == 0 and world == 1:
-        out["spconv"] = bench_spconv(sb, torch, pk)
+        out["spconv"] = bench_spconv(sb, torch, pk, use_graph=not args.no_graph)
         out["reference_gpu_kernel"] = bench_reference_gpu(sb, torch, m, Bs[0], Ds[0])
         out["cpu_baseline"] = cpu_baseline_sample(m, threads=1, budget_s=12.0)
     if dist:
@@ -268,7 +294,7 @@ def run_ours(args):
         print(json.dumps(out))
 
 
-def bench_spconv(sb, torch, pk, steps=300, warmup=20):
+def bench_spconv(sb, torch, pk, steps=300, warmup=20, use_graph=True):
     c = CONV
     f = sb.BlockwiseSpFilter().init_random(c["F"], c["R"], c["S"], c["C"], V_, 1, DENSITY, True, SEED, values="uniform")
     f.transform_and_sync_device()
@@ -281,10 +307,14 @@ def bench_spconv(sb, torch, pk, steps=300, warmup=20):
     for i in range(warmup):
         ops[i % NBc](stream)
     torch.cuda.synchronize()
+    from shflbw_sparse_nn_b200 import _cabi
+    import ctypes as C
+    lib = _cabi.lib()
+    run_steps, G = capture_steps(torch, lambda i, raw: lib.shflbw_spconv_exec(C.byref(ops[i % NBc]._state), raw), steps,
+                                 stream, use_graph=use_graph)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for i in range(steps):
-        ops[i % NBc](stream)
+    run_steps()
     e1.record(stream)
     torch.cuda.synchronize()
     f.device_status()
@@ -296,7 +326,7 @@ def bench_spconv(sb, torch, pk, steps=300, warmup=20):
     return {"workload": "SpConv NHWC 16x14x14x512 -> 2048, 3x3 s1 p1, V=64 density=0.1 filter-permute",
             "us_per_call": round(t * 1e6, 3), "img_per_s": round(c["B"] / t, 1), "nonzero_tflops": round(flops / t / 1e12, 3),
             "dense_equivalent_tflops": round(2.0 * npix * c["C"] * c["R"] * c["S"] * c["F"] / t / 1e12, 2),
-            "launches_per_call": ops[0].launches_per_exec, "t_roof_us": round(t_roof * 1e6, 3),
+            "launches_per_call": ops[0].launches_per_exec, "launch": (f"CUDA graph of {G} calls" if G else "host launches"), "t_roof_us": round(t_roof * 1e6, 3),
             "roofline_frac": round(t_roof / t, 4), "algorithmic_bytes": byt, "nnzb": f.nnzb}
 
 
@@ -398,6 +428,7 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch every timed step from the host instead of replaying a CUDA graph")
     ap.add_argument("--quick", action="store_true",
                     help="profiling aid: timed SpMM loop plus a short SpConv loop only (no e2e, no reference kernels, no CPU baseline)")
     args = ap.parse_args()

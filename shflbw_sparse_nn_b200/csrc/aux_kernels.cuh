@@ -73,37 +73,43 @@ relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, in
     }
 }
 
-// out[q][perm[f]] = staged[q][f] for every output position q; one warp per position.  The
-// permutation sits in shared memory as 16-bit ids (read once per block); each lane moves 8
-// filters at a time with 16-byte global accesses and scatters them into the warp's F-vector
-// in shared memory with 2-byte stores.  Dynamic shared memory: F*2 bytes (perm) + warps*F*2
-// bytes.  F % 8 == 0, F <= 65536.
-constexpr int kUnpermWarps = 8;
+// out[q][perm[f]] = staged[q][f] for every output position q.  A block of 8 warps handles 4
+// positions, two warps each (the kernel is latency-bound: more warps in flight per position
+// shorten it).  The permutation sits in shared memory as 16-bit ids (read once per block);
+// each lane moves 8 filters at a time with 16-byte global accesses and scatters them into the
+// position's F-vector in shared memory with 2-byte stores.  Dynamic shared memory: F*2 bytes
+// (perm) + 4*F*2 bytes.  F % 8 == 0, F <= 65536.
+constexpr int kUnpermWarps = 8, kUnpermPosPerBlock = 4;
 __global__ void __launch_bounds__(kUnpermWarps * 32)
 unpermute_filters(const __half* __restrict__ staged, __half* __restrict__ out, const int* __restrict__ perm,
                   int num_pos, int F) {
     extern __shared__ __align__(16) uint8_t unperm_smem[];
     unsigned short* sperm = (unsigned short*)unperm_smem;        // [F]
-    __half* vec = (__half*)(unperm_smem + (size_t)F * 2);        // [warps][F]
+    __half* vec = (__half*)(unperm_smem + (size_t)F * 2);        // [positions per block][F]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slot = warp >> 1, half_id = warp & 1;              // position slot, which half of its lanes
     for (int f = threadIdx.x; f < F; f += kUnpermWarps * 32) sperm[f] = (unsigned short)__ldg(perm + f);
-    __syncthreads();
-    __half* mine = vec + (size_t)warp * F;
-    for (int q = blockIdx.x * kUnpermWarps + warp; q < num_pos; q += gridDim.x * kUnpermWarps) {
-        const __half* src = staged + (size_t)q * F;
+    __half* mine = vec + (size_t)slot * F;
+    for (int q0 = blockIdx.x * kUnpermPosPerBlock; q0 < num_pos; q0 += gridDim.x * kUnpermPosPerBlock) {
+        const int q = q0 + slot;
+        __syncthreads();                                         // perm loaded / previous vectors read back
+        if (q < num_pos) {
+            const __half* src = staged + (size_t)q * F;
 #pragma unroll 4
-        for (int f8 = lane * 8; f8 < F; f8 += 256) {
-            const uint4 v = *(const uint4*)(src + f8);
-            const uint4 pp = *(const uint4*)(sperm + f8);
-            const __half* h = (const __half*)&v;
-            mine[pp.x & 0xffff] = h[0]; mine[pp.x >> 16] = h[1]; mine[pp.y & 0xffff] = h[2]; mine[pp.y >> 16] = h[3];
-            mine[pp.z & 0xffff] = h[4]; mine[pp.z >> 16] = h[5]; mine[pp.w & 0xffff] = h[6]; mine[pp.w >> 16] = h[7];
+            for (int f8 = (half_id * 32 + lane) * 8; f8 < F; f8 += 512) {
+                const uint4 v = *(const uint4*)(src + f8);
+                const uint4 pp = *(const uint4*)(sperm + f8);
+                const __half* h = (const __half*)&v;
+                mine[pp.x & 0xffff] = h[0]; mine[pp.x >> 16] = h[1]; mine[pp.y & 0xffff] = h[2]; mine[pp.y >> 16] = h[3];
+                mine[pp.z & 0xffff] = h[4]; mine[pp.z >> 16] = h[5]; mine[pp.w & 0xffff] = h[6]; mine[pp.w >> 16] = h[7];
+            }
         }
-        __syncwarp();
-        __half* dst = out + (size_t)q * F;
+        __syncthreads();
+        if (q < num_pos) {
+            __half* dst = out + (size_t)q * F;
 #pragma unroll 4
-        for (int f8 = lane * 8; f8 < F; f8 += 256) *(uint4*)(dst + f8) = *(const uint4*)(mine + f8);
-        __syncwarp();
+            for (int f8 = (half_id * 32 + lane) * 8; f8 < F; f8 += 512) *(uint4*)(dst + f8) = *(const uint4*)(mine + f8);
+        }
     }
 }
 

@@ -289,8 +289,8 @@ static void launch_relayout(const __half* in, __half* staged, int B, int Bp, int
     shflbw::relayout_nhwc_to_chwn<<<grid, 256, 0, s>>>(in, staged, B, Bp, Hin, Win, Hp, Wp, R / 2, S / 2, C);
 }
 
-// Dynamic shared memory of unpermute_filters: 16-bit permutation + one F-vector of fp16 per warp.
-static size_t unperm_smem_bytes(int F) { return (size_t)F * 2 * (1 + shflbw::kUnpermWarps); }
+// Dynamic shared memory of unpermute_filters: 16-bit permutation + one F-vector of fp16 per position.
+static size_t unperm_smem_bytes(int F) { return (size_t)F * 2 * (1 + shflbw::kUnpermPosPerBlock); }
 
 int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap,
                        void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
@@ -400,8 +400,8 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     // 3. inverse filter permutation.
     if (st->staged_out) {
         const int num_pos = st->B * st->Ho * st->Wo;
-        int blocks = (num_pos + shflbw::kUnpermWarps - 1) / shflbw::kUnpermWarps;
-        if (blocks > 148 * 6) blocks = 148 * 6;
+        int blocks = (num_pos + shflbw::kUnpermPosPerBlock - 1) / shflbw::kUnpermPosPerBlock;
+        if (blocks > 148 * 8) blocks = 148 * 8;
         shflbw::unpermute_filters<<<blocks, shflbw::kUnpermWarps * 32, unperm_smem_bytes(st->F), s>>>(
             (const __half*)st->staged_out, (__half*)st->ofmap, st->perm, num_pos, st->F);
     }
