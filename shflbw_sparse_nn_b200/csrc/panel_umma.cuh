@@ -268,6 +268,9 @@ panel_umma_kernel(const PanelParams p) {
 
         int it = 0;        // stage counter across items (all groups count the same sequence)
         int prev_s = -1;   // this group's previous stage, published one iteration later
+#ifdef SHFLBW_COUNTERS
+        long long pc_empty = 0, pc_n = 0, pc_t0 = clock64();
+#endif
         for (int li = cur.li; li < nloc; ++li) {
             const int2 ent = item_tab[li];
             const int num_k = (ent.y + KS - 1) / KS;
@@ -295,10 +298,16 @@ panel_umma_kernel(const PanelParams p) {
                 if ((it % GROUPS) != grp) continue;            // the other group's stage
                 const int s = it % STAGES, s_idx = it % Cfg::IDX_RING;
                 if (it >= STAGES) {  // one lane polls; the warp follows through __syncwarp
+#ifdef SHFLBW_COUNTERS
+                    const long long e0c = clock64();
+#endif
                     if (lane == 0)
                         sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
                                                  SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles, 32);
                     __syncwarp();
+#ifdef SHFLBW_COUNTERS
+                    pc_empty += clock64() - e0c; ++pc_n;
+#endif
                 }
                 if (pw == 0 && lane == 0) TRACE(0, it, 0);
                 if (lane == 0) PTRACE(pidx, it, 0);
@@ -374,6 +383,12 @@ panel_umma_kernel(const PanelParams p) {
         __syncwarp();
         if (lane == 0 && prev_s >= 0) sm100::mbar_arrive(&full_bar[prev_s]);
         if (pw == 0 && lane == 0) CTRACE(2);
+#ifdef SHFLBW_COUNTERS
+        if (lane == 0 && p.trace != nullptr && pidx < 8) {
+            unsigned long long* o = p.trace + 148 * 16 + (blockIdx.x * 8 + pidx) * 4;
+            o[0] = pc_empty; o[1] = pc_n; o[2] = clock64() - pc_t0;
+        }
+#endif
     } else if (warp == 8) {
         // ------------------------------------------------------------ MMA warp ----
         constexpr uint32_t idesc = sm100::make_idesc_f16_mnmajor(128, V);
@@ -391,20 +406,38 @@ panel_umma_kernel(const PanelParams p) {
         // instead of being recomputed by division.
         if (lane == 0) {
             int it = 0;
+#ifdef SHFLBW_COUNTERS
+            long long cnt_wait = 0, cnt_n = 0, cnt_acc = 0, cnt_t0 = clock64();
+#endif
             uint32_t s = 0, ph = 0;     // ring slot of stage `it` and the parity of its full barrier
             bool ready = false;         // that barrier was already seen complete
             for (int li = 0; li < nloc; ++li) {
                 const int rows_total = item_tab[li].y;
                 const int num_k = (rows_total + KS - 1) / KS;
                 const int b = li & 1;
+#ifdef SHFLBW_COUNTERS
+                const long long a0c = clock64();
+#endif
                 if (li >= 2)
                     sm100::mbar_wait_bounded(&acc_empty[b], ((li >> 1) - 1) & 1, cta_abort, p.status_word,
                                              SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 20);
+#ifdef SHFLBW_COUNTERS
+                cnt_acc += clock64() - a0c;
+#endif
                 const uint32_t acc_base = tmem_base + b * Cfg::ACC_COLS;
                 for (int kt = 0; kt < num_k; ++kt, ++it) {
+#ifdef SHFLBW_COUNTERS
+                    if (!ready) {
+                        const long long w0 = clock64();
+                        sm100::mbar_wait_bounded(&full_bar[s], ph, cta_abort, p.status_word,
+                                                 SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
+                        cnt_wait += clock64() - w0; ++cnt_n;
+                    }
+#else
                     if (!ready)
                         sm100::mbar_wait_bounded(&full_bar[s], ph, cta_abort, p.status_word,
                                                  SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
+#endif
                     TRACE(1, it, 0);
                     if (!(ablate & 16)) sm100::fence_proxy_async_smem();  // cp.async (generic proxy) data -> tensor-core (async proxy) reads
                     sm100::tc_fence_after_sync();
@@ -432,6 +465,12 @@ panel_umma_kernel(const PanelParams p) {
                 if (num_k > 0 && !(ablate & 1)) sm100::umma_commit(&acc_full[b]);  // accumulator complete
                 else sm100::mbar_arrive(&acc_full[b]);                             // nothing to wait for
             }
+#ifdef SHFLBW_COUNTERS
+            if (p.trace != nullptr) {
+                unsigned long long* o = p.trace + blockIdx.x * 16;
+                o[0] = cnt_wait; o[1] = cnt_n; o[2] = cnt_acc; o[3] = clock64() - cnt_t0; o[4] = it;
+            }
+#endif
         }
         __syncwarp();
         if (lane == 0) CTRACE(3);

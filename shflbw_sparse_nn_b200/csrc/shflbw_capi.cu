@@ -243,7 +243,7 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
         p.B = (const __half*)st->B; p.C = (const __half*)st->C; p.D = (__half*)st->D; p.N = st->N;
         p.num_items = st->num_items; p.tiles_n = st->tiles_n;
-#ifdef SHFLBW_ABLATE
+#if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
         if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
         if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
 #endif
