@@ -191,7 +191,11 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
     if (beta != 0.f && !C) return SHFLBW_ERR_INVALID_ARG;
     if (!m->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;           // reference: assert(device_synced)
     if (m->bcol != 1) return SHFLBW_ERR_UNSUPPORTED;            // reference: assert(bcol == BK)
-    if (m->brow != 32 && m->brow != 64 && m->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    // Row-block heights 32/64/128 run on the tensor-core kernel.  V = 16 (which the reference
+    // also instantiates, spmm/blockwise_library.cu:15-31) is served by the plain CUDA-core kernel.
+    if (m->brow == 16 && kernel == SHFLBW_KERNEL_AUTO) kernel = SHFLBW_KERNEL_SIMT;
+    if (kernel != SHFLBW_KERNEL_SIMT && m->brow != 32 && m->brow != 64 && m->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    if (kernel == SHFLBW_KERNEL_SIMT && m->nrow > 65535) return SHFLBW_ERR_UNSUPPORTED;   // one grid row per matrix row
     if (N % 8) return SHFLBW_ERR_UNSUPPORTED;                   // 16-byte rows of fp16
     const uintptr_t al = (uintptr_t)B | (uintptr_t)D | (uintptr_t)C;
     if (al & 15) return SHFLBW_ERR_UNSUPPORTED;
@@ -300,12 +304,14 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
     if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
     if (!f->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
-    if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    if (f->brow == 16 && kernel == SHFLBW_KERNEL_AUTO) kernel = SHFLBW_KERNEL_SIMT;   // as for SpMM
+    if (kernel != SHFLBW_KERNEL_SIMT && f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
     if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
     if (((uintptr_t)ifmap | (uintptr_t)ofmap) & 15) return SHFLBW_ERR_UNSUPPORTED;
     const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
     const int Bp = (B + 7) / 8 * 8;
     const long long tokens = (long long)Ho * Wo * Bp;
+    if (kernel == SHFLBW_KERNEL_SIMT && (long long)B * Ho * Wo > 65535) return SHFLBW_ERR_UNSUPPORTED;  // one grid row per position
     // 32-bit element offsets into the staged (halo-padded) input.
     const long long staged_elems = (long long)f->C * (Hin + f->R - 1) * (Win + f->S - 1) * Bp;
     if (tokens >= (1ll << 31) || staged_elems >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;

@@ -111,3 +111,11 @@ def test_host_buffer_call_equals_device_call():
     O_host = np.zeros((8, 10, 10, 128), np.float16)
     sb.spconv_host(f, 8, 10, 10, 1, x, O_host)
     assert np.array_equal(O_host.view(np.uint16), O_dev.view(np.uint16))
+
+
+def test_filter_block_height_16_runs_on_the_cuda_core_kernel():
+    f = sb.BlockwiseSpFilter().init_random(64, 3, 3, 16, 16, 1, 0.3, True, 2, values="uniform")
+    x = sb.uniform_half(716, 4 * 6 * 5 * 16).reshape(4, 6, 5, 16)
+    O, op = run_spconv(f, 4, 6, 5, 1, x)
+    assert op._state.kernel == sb.KERNEL_SIMT and op.launches_per_exec == 1
+    assert_close_fp16(O, _oracle(f, 4, 6, 5, 1, x), what="conv V=16")

@@ -167,3 +167,15 @@ def test_meta_image_equals_reference_transform_and_sync_device():
     r = oa.RefMatrix.init_random(512, 384, 32, 0.15, True, 17)
     m = sb.BlockwiseSpMatrix.from_arrays(512, 384, 32, r.indptr, r.indices, r.values, r.perm)
     assert np.array_equal(m.meta_h, r.meta_image())
+
+
+def test_row_block_height_16_runs_on_the_cuda_core_kernel():
+    """V = 16 (instantiated by the reference, spmm/blockwise_library.cu:15-31) is served by the
+    plain CUDA-core kernel under KERNEL_AUTO; asking for the tensor-core kernel is refused."""
+    m = sb.BlockwiseSpMatrix().init_random(256, 384, 16, 1, 0.2, True, 2021, values="uniform")
+    B = sb.uniform_half(616, 384 * 128).reshape(384, 128)
+    D, op = run_spmm(m, 128, B)
+    assert op._state.kernel == sb.KERNEL_SIMT
+    assert_close_fp16(D, _oracle(m, 128, B), what="V=16")
+    with pytest.raises(sb.ShflbwError):
+        run_spmm(m, 128, B, kernel=sb.KERNEL_TCGEN05)
