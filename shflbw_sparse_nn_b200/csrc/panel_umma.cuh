@@ -74,7 +74,11 @@ struct PanelParams {
 
 // MODE: 0 = SpMM, 1 = SpConv writing NHWC (stored filter order), 2 = SpConv writing the
 // channel-major halo layout the next layer gathers from ("chained" layers).
-constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2;
+// 3 = SpMM with the operands swapped: the block's V rows are the UMMA M dimension (64 or 128
+// TMEM lanes) and the T tokens the N dimension, so ONE instruction per 16 columns covers the
+// whole token tile (the instruction rate, 73 clk minimum each, is what limits this kernel) and
+// the accumulator comes out with an output row per lane.
+constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2, kPanelSpmmRows = 3;
 
 template <int V, int TM, int KS_, int STAGES, int PW, int MODE>
 struct PanelCfg {
@@ -99,7 +103,10 @@ struct PanelCfg {
     static constexpr int IDX_RING = 8;                      // stages of row ids kept in shared memory
     static constexpr int IDX_BYTES = IDX_RING * KS * 4;
     static constexpr int SMEM_BYTES = PIPE_BYTES + OUT_BYTES + BAR_BYTES + TAB_BYTES + IDX_BYTES + 1024;  // + align slack
-    static constexpr uint32_t ACC_COLS = TM * V;            // fp32 columns of one accumulator set
+    static constexpr bool SWAP = MODE == kPanelSpmmRows;
+    static constexpr int KG_BYTES = SWAP ? T * 16 : 2048;   // 8 gathered rows (one K group) of the token tile
+    static constexpr uint32_t ACC_COLS = SWAP ? T : TM * V; // fp32 columns of one accumulator set
+    static_assert(!SWAP || V == 64 || V == 128, "rows-in-lanes needs a legal UMMA M");
     static constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // double buffered
     static_assert(V == 32 || V == 64 || V == 128, "row-block height");
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte swizzle-atom alignment");
@@ -128,8 +135,9 @@ template <int V, int TM, int KS_, int STAGES, int PW, int MODE>
 __global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE>::THREADS, 1)
 panel_umma_kernel(const PanelParams p) {
     using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE>;
-    constexpr bool CONV = MODE != kPanelSpmm;          // implicit-GEMM gather
-    constexpr bool ROWS_OUT = MODE != kPanelConv;      // output rows = block rows / filters, tokens contiguous
+    constexpr bool SWAP = Cfg::SWAP;                                        // rows in TMEM lanes
+    constexpr bool CONV = MODE == kPanelConv || MODE == kPanelConvChain;    // implicit-GEMM gather
+    constexpr bool ROWS_OUT = MODE == kPanelSpmm || MODE == kPanelConvChain; // transposing epilogue: rows out, tokens contiguous
     constexpr int KS = Cfg::KS, T = Cfg::T;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: swizzle atoms are addressed by absolute shared-memory address bits.
@@ -219,7 +227,10 @@ panel_umma_kernel(const PanelParams p) {
         // lane is r = pw*RPW + q*RPI + sub; its swizzled offset splits into a lane constant, a
         // compile-time term in q and one of XT lane-dependent XOR terms.
         const int rbase = pw * RPW + sub;
-        const uint32_t gbase = (uint32_t)((chunk >> 4) * Cfg::G_ACC + (pw * RPW / 8) * 2048 + (((chunk & 15) >> 3)) * 1024);
+        // K group (8 rows) stride and the 64-token swizzle atom inside it.  Tokens as UMMA M: two
+        // 128-token halves, each [K group][2 atoms].  Tokens as UMMA N: [K group][T/64 atoms].
+        const uint32_t gbase = SWAP ? (uint32_t)((pw * RPW / 8) * Cfg::KG_BYTES + (chunk >> 3) * 1024)
+                                    : (uint32_t)((chunk >> 4) * Cfg::G_ACC + (pw * RPW / 8) * 2048 + (((chunk & 15) >> 3)) * 1024);
         uint32_t gx[XT];
 #pragma unroll
         for (int j = 0; j < XT; ++j) {
@@ -350,7 +361,7 @@ panel_umma_kernel(const PanelParams p) {
                     for (int q = 0; q < NQ; ++q) {
                         if (q == NQ / 2) publish_prev();
                         if (rbase + q * RPI < rows_valid && !(ablate & 2))
-                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
+                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * Cfg::KG_BYTES) + gx[q % XT],
                                                lane_src0 + (uint64_t)(uint32_t)idr[q] * row_pitch, nbytes);
                     }
                 } else {
@@ -365,7 +376,7 @@ panel_umma_kernel(const PanelParams p) {
                     for (int q = 0; q < NQ; ++q) {
                         if (q == NQ / 2) publish_prev();
                         if (rbase + q * RPI < rows_valid && !(ablate & 2))
-                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * 2048) + gx[q % XT],
+                            sm100::cp_async_16(st_base + gbase + (uint32_t)(((q * RPI) >> 3) * Cfg::KG_BYTES) + gx[q % XT],
                                                conv_src0 + dq[q], nbytes);
                     }
                 }
@@ -391,11 +402,11 @@ panel_umma_kernel(const PanelParams p) {
 #endif
     } else if (warp == 8) {
         // ------------------------------------------------------------ MMA warp ----
-        constexpr uint32_t idesc = sm100::make_idesc_f16_mnmajor(128, V);
+        constexpr uint32_t idesc = SWAP ? sm100::make_idesc_f16_mnmajor(V, T) : sm100::make_idesc_f16_mnmajor(128, V);
         // Descriptors are built once; per MMA only the 16-byte-granular start address field
         // (low bits) advances.  A single thread issues every MMA, so scalar work between two
         // tcgen05.mma instructions directly limits the tensor-pipe issue rate.
-        const uint64_t gdesc0 = sm100::make_smem_desc(smem_base, 1024, 2048, sm100::kSwizzle128B);
+        const uint64_t gdesc0 = sm100::make_smem_desc(smem_base, 1024, Cfg::KG_BYTES, sm100::kSwizzle128B);
         const uint64_t wdesc0 =
             V == 32 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 512, 512, sm100::kSwizzle64B)
           : V == 64 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 1024, sm100::kSwizzle128B)
@@ -448,10 +459,14 @@ panel_umma_kernel(const PanelParams p) {
                     uint32_t accum = (uint32_t)(kt != 0);
 #pragma unroll 1
                     for (int j = 0; j < nk; ++j) {
+                        if constexpr (SWAP) {
+                            sm100::umma_f16_ss(acc_base, wdj, gdj, idesc, accum);   // D[row][token] += W^T . G
+                        } else {
 #pragma unroll
-                        for (int a = 0; a < TM; ++a)
-                            sm100::umma_f16_ss(acc_base + a * V, gdj + (uint64_t)((a * Cfg::G_ACC) >> 4), wdj, idesc, accum);
-                        gdj += 4096 >> 4;
+                            for (int a = 0; a < TM; ++a)
+                                sm100::umma_f16_ss(acc_base + a * V, gdj + (uint64_t)((a * Cfg::G_ACC) >> 4), wdj, idesc, accum);
+                        }
+                        gdj += (2 * Cfg::KG_BYTES) >> 4;
                         wdj += WSTEP >> 4;
                         accum = 1u;
                     }
@@ -496,6 +511,80 @@ panel_umma_kernel(const PanelParams p) {
             __syncwarp();
             sm100::tc_fence_after_sync();
             if (tid == 0) TRACE(2, li, 0);
+            if constexpr (SWAP) {
+                // Rows in lanes: lane l of quadrant `quad` holds output row m of the block (V = 64:
+                // the quadrant's first 16 lanes, m = 16*quad + l; V = 128: all 32, m = 32*quad + l)
+                // and this warp reads token columns [half_id*T/2, +T/2), 32 at a time: a lane's 32
+                // tokens are 64 contiguous bytes of its D row.  They are packed to fp16, staged
+                // row by row in a swizzled shared-memory tile and stored 16 bytes per lane with
+                // four lanes per row, so that a store instruction touches 8 rows x 64 bytes.
+                constexpr int LR = V == 64 ? 16 : 32;                    // rows (valid lanes) per quadrant
+                constexpr int HC = T / 2;                                // token columns of this warp
+                uint8_t* tile = smem + Cfg::PIPE_BYTES + warp * 2048;    // [LR rows][64 bytes]
+                const uint32_t acc0 = tmem_base + ((uint32_t)(quad * 32) << 16) + b * Cfg::ACC_COLS + half_id * HC;
+                const int m = quad * LR + (lane < LR ? lane : 0);
+                const int drow = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
+                const uint32_t my_roff = (uint32_t)drow * (uint32_t)p.N;
+                uint32_t roff[LR / 8];                                   // D offsets of rows 8i + lane/4
+#pragma unroll
+                for (int i = 0; i < LR / 8; ++i) roff[i] = __shfl_sync(0xffffffffu, my_roff, i * 8 + (lane >> 2));
+                const bool use_c = p.beta != 0.0f && p.C != nullptr;
+#pragma unroll 1
+                for (int cc = 0; cc < HC; cc += 32) {
+                    uint32_t r[32];
+                    if (has_k) {
+                        sm100::tmem_ld_32x32b_x32(acc0 + cc, r);
+                        sm100::tmem_ld_wait();
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) r[e] = 0u;
+                    }
+                    if (cc + 32 >= HC) {  // last TMEM read of this item by this warp: release the buffer
+                        sm100::tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
+                        if (tid == 0) TRACE(2, li, 1);
+                    }
+                    if (lane < LR) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint4 v;
+                            __half2* h = (__half2*)&v;
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                // same arithmetic as the reference: round to fp16, then alpha in fp16
+                                h[e] = __floats2half2_rn(__uint_as_float(r[c * 8 + 2 * e]), __uint_as_float(r[c * 8 + 2 * e + 1]));
+                                if (!use_c) h[e] = __hmul2(h[e], alpha2);
+                            }
+                            *(uint4*)(tile + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = v;
+                        }
+                    }
+                    __syncwarp();
+                    if (!(ablate & 512)) {
+                        const int c = lane & 3;
+                        const int tok_g = n0 + half_id * HC + cc + c * 8;    // this lane's 8 tokens
+#pragma unroll
+                        for (int i = 0; i < LR / 8; ++i) {
+                            const int row = i * 8 + (lane >> 2);
+                            uint4 v = *(const uint4*)(tile + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
+                            if (tok_g < p.N && !(ablate & 8)) {
+                                const size_t off = (size_t)roff[i] + (size_t)tok_g;
+                                if (use_c) {
+                                    const uint4 cv = *(const uint4*)(p.C + off);
+                                    __half* h = (__half*)&v;
+                                    const __half* ch = (const __half*)&cv;
+#pragma unroll
+                                    for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
+                                }
+                                *(uint4*)(p.D + off) = v;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
+                if (tid == 0) TRACE(2, li, 3);
+                continue;
+            }
             // columns [col0, col0 + COLS) of the accumulator set: accumulator a = col / V, row m = col % V
             const int col0 = half_id * COLS;
             const uint32_t acc_base = tmem_base + ((uint32_t)(quad * 32) << 16) + b * Cfg::ACC_COLS + col0;

@@ -53,14 +53,24 @@ PanelChoice choice() {
 // and bring nothing.
 template <int MODE>
 bool lookup(int V, int tile, PanelChoice* out) {
-    switch (V * 1000 + tile) {
-        case 32128:  *out = choice<32, 1, 64, 8, 8, MODE>(); return true;    // 20 KB stages
-        case 32256:  *out = choice<32, 2, 64, 5, 8, MODE>(); return true;    // 36 KB
-        case 64128:  *out = choice<64, 1, 64, 8, 8, MODE>(); return true;    // 24 KB
-        case 64256:  *out = choice<64, 2, 64, 5, 8, MODE>(); return true;    // 40 KB
-        case 128128: *out = choice<128, 1, 64, 6, 8, MODE>(); return true;   // 32 KB
-        case 128256: *out = choice<128, 2, 64, 4, 8, MODE>(); return true;   // 48 KB
-        default: return false;
+    if constexpr (MODE == shflbw::kPanelSpmmRows) {           // rows in TMEM lanes: V must be a legal UMMA M
+        switch (V * 1000 + tile) {
+            case 64128:  *out = choice<64, 1, 64, 8, 8, MODE>(); return true;
+            case 64256:  *out = choice<64, 2, 64, 5, 8, MODE>(); return true;
+            case 128128: *out = choice<128, 1, 64, 6, 8, MODE>(); return true;
+            case 128256: *out = choice<128, 2, 64, 4, 8, MODE>(); return true;
+            default: return false;
+        }
+    } else {
+        switch (V * 1000 + tile) {
+            case 32128:  *out = choice<32, 1, 64, 8, 8, MODE>(); return true;    // 20 KB stages
+            case 32256:  *out = choice<32, 2, 64, 5, 8, MODE>(); return true;    // 36 KB
+            case 64128:  *out = choice<64, 1, 64, 8, 8, MODE>(); return true;    // 24 KB
+            case 64256:  *out = choice<64, 2, 64, 5, 8, MODE>(); return true;    // 40 KB
+            case 128128: *out = choice<128, 1, 64, 6, 8, MODE>(); return true;   // 32 KB
+            case 128256: *out = choice<128, 2, 64, 4, 8, MODE>(); return true;   // 48 KB
+            default: return false;
+        }
     }
 }
 
@@ -93,8 +103,15 @@ int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
     const long long waves256 = (items256 + sms - 1) / sms, waves128 = (items128 + sms - 1) / sms;
     if (n_tokens <= 128 || waves128 * 2 < waves256 * 3) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
-    if (!lookup<MODE>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
-    out->variant = 0;
+    // SpMM with V = 64 / 128 runs with the operands swapped (rows in TMEM lanes, one MMA per 16
+    // columns for the whole token tile); SHFLBW_SWAP=0 selects the tokens-in-lanes kernel (tuning aid).
+    bool swapped = false;
+    if constexpr (MODE == shflbw::kPanelSpmm) {
+        const char* e = getenv("SHFLBW_SWAP");
+        if ((V == 64 || V == 128) && !(e && atoi(e) == 0)) swapped = lookup<shflbw::kPanelSpmmRows>(V, tile, out);
+    }
+    if (!swapped && !lookup<MODE>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
+    out->variant = swapped ? 1 : 0;
     CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
     return SHFLBW_OK;
 }
@@ -241,7 +258,9 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         // The state is a POD and may have been copied: re-derive the function pointer from the
         // recorded configuration (the shared-memory attribute was set at init).
         PanelChoice ch;
-        if (!lookup<shflbw::kPanelSpmm>(st->V, st->tokens_per_cta, &ch)) return SHFLBW_ERR_INVALID_ARG;
+        const bool found = st->variant == 1 ? lookup<shflbw::kPanelSpmmRows>(st->V, st->tokens_per_cta, &ch)
+                                            : lookup<shflbw::kPanelSpmm>(st->V, st->tokens_per_cta, &ch);
+        if (!found) return SHFLBW_ERR_INVALID_ARG;
         shflbw::PanelParams p{};
         p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
