@@ -78,7 +78,8 @@ struct PanelParams {
 // TMEM lanes) and the T tokens the N dimension, so ONE instruction per 16 columns covers the
 // whole token tile (the instruction rate, 73 clk minimum each, is what limits this kernel) and
 // the accumulator comes out with an output row per lane.
-constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2, kPanelSpmmRows = 3;
+// 4 = chained SpConv with the operands swapped in the same way.
+constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2, kPanelSpmmRows = 3, kPanelConvChainRows = 4;
 
 template <int V, int TM, int KS_, int STAGES, int PW, int MODE>
 struct PanelCfg {
@@ -103,7 +104,7 @@ struct PanelCfg {
     static constexpr int IDX_RING = 8;                      // stages of row ids kept in shared memory
     static constexpr int IDX_BYTES = IDX_RING * KS * 4;
     static constexpr int SMEM_BYTES = PIPE_BYTES + OUT_BYTES + BAR_BYTES + TAB_BYTES + IDX_BYTES + 1024;  // + align slack
-    static constexpr bool SWAP = MODE == kPanelSpmmRows;
+    static constexpr bool SWAP = MODE == kPanelSpmmRows || MODE == kPanelConvChainRows;
     static constexpr int KG_BYTES = SWAP ? T * 16 : 2048;   // 8 gathered rows (one K group) of the token tile
     static constexpr uint32_t ACC_COLS = SWAP ? T : TM * V; // fp32 columns of one accumulator set
     static_assert(!SWAP || V == 64 || V == 128, "rows-in-lanes needs a legal UMMA M");
@@ -136,7 +137,8 @@ __global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE>::THREAD
 panel_umma_kernel(const PanelParams p) {
     using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE>;
     constexpr bool SWAP = Cfg::SWAP;                                        // rows in TMEM lanes
-    constexpr bool CONV = MODE == kPanelConv || MODE == kPanelConvChain;    // implicit-GEMM gather
+    constexpr bool CONV = MODE == kPanelConv || MODE == kPanelConvChain || MODE == kPanelConvChainRows;  // implicit-GEMM gather
+    constexpr bool CHAIN = MODE == kPanelConvChain || MODE == kPanelConvChainRows;
     constexpr bool ROWS_OUT = MODE == kPanelSpmm || MODE == kPanelConvChain; // transposing epilogue: rows out, tokens contiguous
     constexpr int KS = Cfg::KS, T = Cfg::T;
     extern __shared__ uint8_t smem_raw[];
@@ -523,12 +525,19 @@ panel_umma_kernel(const PanelParams p) {
                 uint8_t* tile = smem + Cfg::PIPE_BYTES + warp * 2048;    // [LR rows][64 bytes]
                 const uint32_t acc0 = tmem_base + ((uint32_t)(quad * 32) << 16) + b * Cfg::ACC_COLS + half_id * HC;
                 const int m = quad * LR + (lane < LR ? lane : 0);
-                const int drow = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
-                const uint32_t my_roff = (uint32_t)drow * (uint32_t)p.N;
+                uint32_t my_roff;                                        // element offset of this lane's output row
+                if constexpr (CHAIN) {
+                    my_roff = (uint32_t)(blk * V + m) * (uint32_t)p.out_plane;   // stored filter order
+                } else {
+                    const int drow = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
+                    my_roff = (uint32_t)drow * (uint32_t)p.N;
+                }
+                __half* const obase = CHAIN ? p.out : p.D;
+                const __half2 zero2 = __float2half2_rn(0.f);
                 uint32_t roff[LR / 8];                                   // D offsets of rows 8i + lane/4
 #pragma unroll
                 for (int i = 0; i < LR / 8; ++i) roff[i] = __shfl_sync(0xffffffffu, my_roff, i * 8 + (lane >> 2));
-                const bool use_c = p.beta != 0.0f && p.C != nullptr;
+                const bool use_c = !CHAIN && p.beta != 0.0f && p.C != nullptr;
 #pragma unroll 1
                 for (int cc = 0; cc < HC; cc += 32) {
                     uint32_t r[32];
@@ -555,6 +564,7 @@ panel_umma_kernel(const PanelParams p) {
                                 // same arithmetic as the reference: round to fp16, then alpha in fp16
                                 h[e] = __floats2half2_rn(__uint_as_float(r[c * 8 + 2 * e]), __uint_as_float(r[c * 8 + 2 * e + 1]));
                                 if (!use_c) h[e] = __hmul2(h[e], alpha2);
+                                if (CHAIN && p.relu) h[e] = __hmax2(h[e], zero2);
                             }
                             *(uint4*)(tile + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = v;
                         }
@@ -563,12 +573,20 @@ panel_umma_kernel(const PanelParams p) {
                     if (!(ablate & 512)) {
                         const int c = lane & 3;
                         const int tok_g = n0 + half_id * HC + cc + c * 8;    // this lane's 8 tokens
+                        uint32_t goff = (uint32_t)tok_g;                     // their offset inside an output row
+                        if constexpr (CHAIN) {   // 8 images of one output pixel in the consumer's halo-padded plane
+                            if (tok_g < p.N) {
+                                const int pix = tok_g / p.Bp, nn = tok_g - pix * p.Bp;
+                                const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                                goff = (uint32_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
+                            }
+                        }
 #pragma unroll
                         for (int i = 0; i < LR / 8; ++i) {
                             const int row = i * 8 + (lane >> 2);
                             uint4 v = *(const uint4*)(tile + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
                             if (tok_g < p.N && !(ablate & 8)) {
-                                const size_t off = (size_t)roff[i] + (size_t)tok_g;
+                                const size_t off = (size_t)roff[i] + (size_t)goff;
                                 if (use_c) {
                                     const uint4 cv = *(const uint4*)(p.C + off);
                                     __half* h = (__half*)&v;
@@ -576,7 +594,7 @@ panel_umma_kernel(const PanelParams p) {
 #pragma unroll
                                     for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
                                 }
-                                *(uint4*)(p.D + off) = v;
+                                *(uint4*)(obase + off) = v;
                             }
                         }
                     }

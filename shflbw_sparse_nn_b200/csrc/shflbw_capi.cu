@@ -53,7 +53,7 @@ PanelChoice choice() {
 // and bring nothing.
 template <int MODE>
 bool lookup(int V, int tile, PanelChoice* out) {
-    if constexpr (MODE == shflbw::kPanelSpmmRows) {           // rows in TMEM lanes: V must be a legal UMMA M
+    if constexpr (MODE == shflbw::kPanelSpmmRows || MODE == shflbw::kPanelConvChainRows) {   // rows in TMEM lanes: V must be a legal UMMA M
         switch (V * 1000 + tile) {
             case 64128:  *out = choice<64, 1, 64, 8, 8, MODE>(); return true;
             case 64256:  *out = choice<64, 2, 64, 5, 8, MODE>(); return true;
@@ -92,7 +92,7 @@ int sm_count() {
 // the default; 128 is used when the dense extent is too small to give every SM a few items.
 // SHFLBW_TILE=128|256 overrides (tuning aid).
 template <int MODE>
-int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
+int pick_panel(int V, long long n_tokens, int row_blocks, long long padded_cols, PanelChoice* out) {
     // Token tile: a persistent CTA works through ceil(items / SMs) items in turn; an item of
     // the 128-token tile was measured at ~2/3 of the time of a 256-token item (half the
     // gathered bytes, the same number of pipeline stages).
@@ -103,12 +103,19 @@ int pick_panel(int V, long long n_tokens, int row_blocks, PanelChoice* out) {
     const long long waves256 = (items256 + sms - 1) / sms, waves128 = (items128 + sms - 1) / sms;
     if (n_tokens <= 128 || waves128 * 2 < waves256 * 3) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
-    // SpMM with V = 64 / 128 runs with the operands swapped (rows in TMEM lanes, one MMA per 16
-    // columns for the whole token tile); SHFLBW_SWAP=0 selects the tokens-in-lanes kernel (tuning aid).
+    // SpMM and chained SpConv with V = 64 / 128 can run with the operands swapped (rows in TMEM
+    // lanes, one MMA per 16 columns for the whole token tile); SHFLBW_SWAP=0|1 forces the choice
+    // (tuning aid).
     bool swapped = false;
-    if constexpr (MODE == shflbw::kPanelSpmm) {
+    if constexpr (MODE == shflbw::kPanelSpmm || MODE == shflbw::kPanelConvChain) {
         const char* e = getenv("SHFLBW_SWAP");
-        if ((V == 64 || V == 128) && !(e && atoi(e) == 0)) swapped = lookup<shflbw::kPanelSpmmRows>(V, tile, out);
+        // Worth it when the main loop dominates an item (>= 3 pipeline stages of non-zero columns
+        // per block on average); with fewer columns the item is all epilogue, and the
+        // rows-in-lanes epilogue of a 64-row block keeps only half of each warp's lanes busy.
+        const bool deep = padded_cols >= 192ll * row_blocks;
+        if ((V == 64 || V == 128) && (e ? atoi(e) != 0 : deep))
+            swapped = MODE == shflbw::kPanelSpmm ? lookup<shflbw::kPanelSpmmRows>(V, tile, out)
+                                                 : lookup<shflbw::kPanelConvChainRows>(V, tile, out);
     }
     if (!swapped && !lookup<MODE>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
     out->variant = swapped ? 1 : 0;
@@ -231,7 +238,7 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
         out->tokens_per_cta = 128; out->stages = 0; out->shared_mem_size = 0;
     } else {
         PanelChoice ch;
-        int rc = pick_panel<shflbw::kPanelSpmm>(m->brow, N, out->num_row_blocks, &ch);
+        int rc = pick_panel<shflbw::kPanelSpmm>(m->brow, N, out->num_row_blocks, m->kptr.empty() ? 0 : m->kptr.back(), &ch);
         if (rc != SHFLBW_OK) return rc;
         out->kernel = SHFLBW_KERNEL_TCGEN05;
         out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
@@ -353,7 +360,7 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
         return SHFLBW_OK;
     }
     PanelChoice ch;
-    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, &ch);
+    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
     if (rc != SHFLBW_OK) return rc;
     out->kernel = SHFLBW_KERNEL_TCGEN05;
     out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
@@ -393,8 +400,9 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
         return SHFLBW_OK;
     }
     PanelChoice ch;
-    const bool ok_kernel = st->chain ? lookup<shflbw::kPanelConvChain>(st->V, st->tokens_per_cta, &ch)
-                                     : lookup<shflbw::kPanelConv>(st->V, st->tokens_per_cta, &ch);
+    const bool ok_kernel = !st->chain        ? lookup<shflbw::kPanelConv>(st->V, st->tokens_per_cta, &ch)
+                           : st->variant == 1 ? lookup<shflbw::kPanelConvChainRows>(st->V, st->tokens_per_cta, &ch)
+                                              : lookup<shflbw::kPanelConvChain>(st->V, st->tokens_per_cta, &ch);
     if (!ok_kernel) return SHFLBW_ERR_INVALID_ARG;
     // 1. NHWC -> channel-major, batch-innermost staging with a zero halo (chained layers get
     //    their input in that layout already).
@@ -527,7 +535,7 @@ int shflbw_spconv_chain_init(shflbw_matrix_t* f, int B, int Hin, int Win, int st
     out->perm = f->d_perm; out->status_word = f->d_status;
     out->chain = 1; out->out_R = R_next; out->out_S = S_next; out->relu = relu != 0;
     PanelChoice ch;
-    int rc = pick_panel<shflbw::kPanelConvChain>(f->brow, tokens, f->F / f->brow, &ch);
+    int rc = pick_panel<shflbw::kPanelConvChain>(f->brow, tokens, f->F / f->brow, f->kptr.empty() ? 0 : f->kptr.back(), &ch);
     if (rc != SHFLBW_OK) return rc;
     out->kernel = SHFLBW_KERNEL_TCGEN05;
     out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
@@ -583,7 +591,7 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     shflbw_spconv_state_t st;
     std::memset(&st, 0, sizeof st);
     PanelChoice ch;
-    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, &ch);
+    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
     if (rc != SHFLBW_OK) return rc;
     const int sms = sm_count();
     if (sms <= 0) return SHFLBW_ERR_CUDA;

@@ -36,6 +36,24 @@ def tile(tokens):
             os.environ["SHFLBW_TILE"] = old
 
 
+@contextmanager
+def operand_swap(mode):
+    """Force (1) or forbid (0) the rows-in-lanes kernels for ops initialised inside the block;
+    None leaves the library's own choice."""
+    old = os.environ.get("SHFLBW_SWAP")
+    if mode is None:
+        os.environ.pop("SHFLBW_SWAP", None)
+    else:
+        os.environ["SHFLBW_SWAP"] = str(int(mode))
+    try:
+        yield
+    finally:
+        if old is None:
+            os.environ.pop("SHFLBW_SWAP", None)
+        else:
+            os.environ["SHFLBW_SWAP"] = old
+
+
 def run_spmm(m, N, B, alpha=1.0, Cm=None, beta=0.0, kernel=sb.KERNEL_AUTO, tokens=None, poison=True):
     """D = alpha*A.B + beta*C on the GPU through SpmmBlockwiseOp; returns D as numpy fp16."""
     m.transform_and_sync_device()

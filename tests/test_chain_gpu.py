@@ -10,7 +10,7 @@ import torch
 import oracle_api as oa
 import shflbw_sparse_nn_b200 as sb
 from conftest import assert_close_fp16
-from gpu_util import dev, host, run_spconv
+from gpu_util import dev, host, operand_swap, run_spconv
 
 pytestmark = pytest.mark.gpu
 
@@ -19,8 +19,9 @@ def _chain_buf(C_, H, W, B, R, S):
     return torch.zeros(sb.chain_buffer_elems(C_, H, W, B, R, S), dtype=torch.float16, device="cuda")
 
 
-@pytest.mark.parametrize("V,Bn,relu", [(32, 8, False), (64, 3, True), (128, 16, True)])
-def test_one_chained_layer_equals_the_unchained_layer_bit_for_bit(V, Bn, relu):
+@pytest.mark.parametrize("V,Bn,relu,swap", [(32, 8, False, None), (64, 3, True, 0), (64, 3, True, 1), (128, 16, True, 0),
+                                             (128, 16, False, 1)])
+def test_one_chained_layer_equals_the_unchained_layer_bit_for_bit(V, Bn, relu, swap):
     H, W, Cc, F = 9, 7, 32, 2 * V
     f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, V, 1, 0.25, True, 11 + V, values="uniform")
     x = sb.uniform_half(500 + V, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
@@ -32,8 +33,9 @@ def test_one_chained_layer_equals_the_unchained_layer_bit_for_bit(V, Bn, relu):
     y = torch.full((Bn, H, W, F), float("nan"), dtype=torch.float16, device="cuda")
     s = torch.cuda.current_stream()
     sb.chain_import_nhwc(xd, Bn, H, W, Cc, 3, 3, b0, s)
-    op = sb.SpconvChainOp().initialize(f, Bn, H, W, 1, b0, b1, 1, 1, relu=relu)
-    assert op.launches_per_exec == 1
+    with operand_swap(swap):          # both kernel orientations (rows or tokens in TMEM lanes)
+        op = sb.SpconvChainOp().initialize(f, Bn, H, W, 1, b0, b1, 1, 1, relu=relu)
+    assert op.launches_per_exec == 1 and (swap is None or op._state.variant == swap)
     for _ in range(2):                                          # buffers are reusable without re-zeroing
         op(s)
     sb.chain_export_nhwc(b1, Bn, H, W, F, 1, 1, f, y, s)

@@ -13,7 +13,7 @@ import torch
 import oracle_api as oa
 import shflbw_sparse_nn_b200 as sb
 from conftest import assert_close_fp16
-from gpu_util import dev, host, run_spmm
+from gpu_util import dev, host, operand_swap, run_spmm
 
 pytestmark = pytest.mark.gpu
 
@@ -179,3 +179,22 @@ def test_row_block_height_16_runs_on_the_cuda_core_kernel():
     assert_close_fp16(D, _oracle(m, 128, B), what="V=16")
     with pytest.raises(sb.ShflbwError):
         run_spmm(m, 128, B, kernel=sb.KERNEL_TCGEN05)
+
+
+@pytest.mark.parametrize("V", [64, 128])
+@pytest.mark.parametrize("swap", [0, 1])
+@pytest.mark.parametrize("tokens", [128, 256])
+def test_both_operand_orientations(V, swap, tokens):
+    """V = 64 / 128 have two kernels: tokens in TMEM lanes (UMMA M = 128 tokens, N = V) and rows in
+    TMEM lanes (M = V, N = the token tile).  Both must match the oracle, with a ragged dense width,
+    empty and short row blocks, alpha and beta."""
+    M, K, N = 4 * V, 640, 1000
+    m = sb.BlockwiseSpMatrix().init_random(M, K, V, 1, 0.35, True, 900 + V, values="uniform")
+    B = sb.uniform_half(901, K * N).reshape(K, N)
+    Cm = sb.uniform_half(902, M * N).reshape(M, N)
+    with operand_swap(swap):
+        D, op = run_spmm(m, N, B, alpha=0.5, Cm=Cm, beta=-1.5, tokens=tokens)
+        D2, op2 = run_spmm(m, N, B, tokens=tokens)
+    assert op._state.variant == swap and op2._state.variant == swap
+    assert_close_fp16(D, _oracle(m, N, B, 0.5, Cm, -1.5), what=f"V={V} swap={swap} alpha/beta")
+    assert_close_fp16(D2, _oracle(m, N, B), what=f"V={V} swap={swap}")
