@@ -73,30 +73,36 @@ relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, in
     }
 }
 
-// out[q][perm[f]] = staged[q][f] for every output position q.  A block of 8 warps handles 4
-// positions, two warps each (the kernel is latency-bound: more warps in flight per position
-// shorten it).  The permutation sits in shared memory as 16-bit ids (read once per block);
-// each lane moves 8 filters at a time with 16-byte global accesses and scatters them into the
-// position's F-vector in shared memory with 2-byte stores.  Dynamic shared memory: F*2 bytes
-// (perm) + 4*F*2 bytes.  F % 8 == 0, F <= 65536.
-constexpr int kUnpermWarps = 8, kUnpermPosPerBlock = 4;
-__global__ void __launch_bounds__(kUnpermWarps * 32)
+// out[q][perm[f]] = staged[q][f] for every output position q.  G = clamp(F/8, 8, 64) threads
+// share one position (each moves 8 filters at a time with 16-byte global accesses), so a block
+// of 256 threads handles 256/G positions at once: 4 for F >= 512 (two warps each -- the kernel
+// is latency-bound and more warps per position shorten it) up to 32 for F = 64.  The
+// permutation sits in shared memory as 16-bit ids (read once per block); values are scattered
+// into the position's F-vector in shared memory with 2-byte stores and leave as 16-byte stores.
+// Dynamic shared memory: F*2 bytes (perm) + (256/G)*F*2 bytes.  F % 8 == 0, F <= 65536.
+constexpr int kUnpermThreads = 256;
+__host__ __device__ inline int unperm_threads_per_pos(int F) {
+    int g = 8;
+    while (g < 64 && g * 8 < F) g *= 2;
+    return g;
+}
+__global__ void __launch_bounds__(kUnpermThreads)
 unpermute_filters(const __half* __restrict__ staged, __half* __restrict__ out, const int* __restrict__ perm,
                   int num_pos, int F) {
     extern __shared__ __align__(16) uint8_t unperm_smem[];
     unsigned short* sperm = (unsigned short*)unperm_smem;        // [F]
     __half* vec = (__half*)(unperm_smem + (size_t)F * 2);        // [positions per block][F]
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int slot = warp >> 1, half_id = warp & 1;              // position slot, which half of its lanes
-    for (int f = threadIdx.x; f < F; f += kUnpermWarps * 32) sperm[f] = (unsigned short)__ldg(perm + f);
+    const int G = unperm_threads_per_pos(F), P = kUnpermThreads / G;
+    const int slot = threadIdx.x / G, t = threadIdx.x - slot * G;   // position slot, thread within it
+    for (int f = threadIdx.x; f < F; f += kUnpermThreads) sperm[f] = (unsigned short)__ldg(perm + f);
     __half* mine = vec + (size_t)slot * F;
-    for (int q0 = blockIdx.x * kUnpermPosPerBlock; q0 < num_pos; q0 += gridDim.x * kUnpermPosPerBlock) {
+    for (int q0 = blockIdx.x * P; q0 < num_pos; q0 += gridDim.x * P) {
         const int q = q0 + slot;
         __syncthreads();                                         // perm loaded / previous vectors read back
         if (q < num_pos) {
             const __half* src = staged + (size_t)q * F;
 #pragma unroll 4
-            for (int f8 = (half_id * 32 + lane) * 8; f8 < F; f8 += 512) {
+            for (int f8 = t * 8; f8 < F; f8 += G * 8) {
                 const uint4 v = *(const uint4*)(src + f8);
                 const uint4 pp = *(const uint4*)(sperm + f8);
                 const __half* h = (const __half*)&v;
@@ -108,7 +114,7 @@ unpermute_filters(const __half* __restrict__ staged, __half* __restrict__ out, c
         if (q < num_pos) {
             __half* dst = out + (size_t)q * F;
 #pragma unroll 4
-            for (int f8 = (half_id * 32 + lane) * 8; f8 < F; f8 += 512) *(uint4*)(dst + f8) = *(const uint4*)(mine + f8);
+            for (int f8 = t * 8; f8 < F; f8 += G * 8) *(uint4*)(dst + f8) = *(const uint4*)(mine + f8);
         }
     }
 }

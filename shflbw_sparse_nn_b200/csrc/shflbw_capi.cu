@@ -320,7 +320,9 @@ static void launch_relayout(const __half* in, __half* staged, int B, int Bp, int
 }
 
 // Dynamic shared memory of unpermute_filters: 16-bit permutation + one F-vector of fp16 per position.
-static size_t unperm_smem_bytes(int F) { return (size_t)F * 2 * (1 + shflbw::kUnpermPosPerBlock); }
+static size_t unperm_smem_bytes(int F) {
+    return (size_t)F * 2 * (1 + shflbw::kUnpermThreads / shflbw::unperm_threads_per_pos(F));
+}
 
 int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap,
                        void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
@@ -433,9 +435,10 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     // 3. inverse filter permutation.
     if (st->staged_out) {
         const int num_pos = st->B * st->Ho * st->Wo;
-        int blocks = (num_pos + shflbw::kUnpermPosPerBlock - 1) / shflbw::kUnpermPosPerBlock;
-        if (blocks > 148 * 8) blocks = 148 * 8;
-        shflbw::unpermute_filters<<<blocks, shflbw::kUnpermWarps * 32, unperm_smem_bytes(st->F), s>>>(
+        const int per_block = shflbw::kUnpermThreads / shflbw::unperm_threads_per_pos(st->F);
+        int blocks = (num_pos + per_block - 1) / per_block;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        shflbw::unpermute_filters<<<blocks, shflbw::kUnpermThreads, unperm_smem_bytes(st->F), s>>>(
             (const __half*)st->staged_out, (__half*)st->ofmap, st->perm, num_pos, st->F);
     }
     CK(cudaGetLastError());
