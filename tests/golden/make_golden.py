@@ -29,7 +29,10 @@ sys.path.insert(0, str(HERE.parent.parent))
 import oracle_api as oa  # noqa: E402
 from shflbw_sparse_nn_b200.blockwise import uniform_half  # noqa: E402
 
-REF_GOLDEN = Path("/root/reference/example/mtx_dump.txt")
+import os  # noqa: E402
+
+# checkout of the reference project (same default as oracle/Makefile's REF)
+REF_GOLDEN = Path(os.environ.get("REF", "/root/reference")) / "example" / "mtx_dump.txt"
 
 BUILDER_GRID = [
     # nrow, ncol, brow, density, permute, seed
