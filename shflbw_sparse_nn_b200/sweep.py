@@ -13,7 +13,10 @@ the HBM peak).  `resnet50` times every pruned 1x1 / 3x3 layer shape of the ResNe
 forward pass (each distinct shape weighted by how often the [3,4,6,3] stack uses it; the dense
 7x7 stem and the pooling / classifier layers are not part of the sparse path and not timed).
 With --chained every layer runs as a chained layer (activations stay channel-major, halo-padded
-and in stored filter order between layers; one launch per layer, ReLU fused).
+and in stored filter order between layers; one launch per layer, ReLU fused).  Launched with
+`python -m torch.distributed.run --nproc-per-node G --master-addr 127.0.0.1 -m
+shflbw_sparse_nn_b200.sweep resnet50 ...` the batch is split over G GPUs (filters replicated, no
+exchange) and the per-layer time is the maximum over the ranks.
 
 Timing follows the reference's tool (benchmark/benchmark.spmm.cu:36-49): warm-up launches,
 then the mean over `reps` launches between two CUDA events.  Inputs alternate between buffers
@@ -97,9 +100,21 @@ def sweep_spmm(args, sb, torch):
 
 
 def sweep_resnet50(args, sb, torch):
+    """Under torchrun (WORLD_SIZE > 1, one rank per GPU) the batch is split evenly over the ranks
+    -- the path shards along the batch with the filters replicated and no exchange -- and every
+    layer's time is the maximum over the ranks; rank 0 prints."""
+    import os
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+        dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+        if args.batch % world:
+            raise SystemExit("--batch must be divisible by the number of ranks")
     rows, total = [], 0.0
-    gen = torch.Generator(device="cuda").manual_seed(11)
-    Bn = args.batch
+    gen = torch.Generator(device="cuda").manual_seed(11 + rank)
+    Bn = args.batch // world
     for (Ho, Wo, Cc, F, R, S, stride, uses) in RESNET50_LAYERS:
         Hin, Win = Ho * stride, Wo * stride
         f = sb.BlockwiseSpFilter().init_random(F, R, S, Cc, 64, 1, 0.2, True, 2021, values="uniform")
@@ -123,8 +138,14 @@ def sweep_resnet50(args, sb, torch):
                    for i in range(nb)]
         else:
             ops = [sb.SpconvBlockwiseOp().initialize(f, Bn, Hin, Win, stride, xs[i], os_[i]) for i in range(nb)]
+        if dist:
+            dist.barrier()
         t = _time(torch, ops, args.reps)
         f.device_status()
+        if dist:
+            tt = torch.tensor([t], device="cuda", dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            t = float(tt.item())
         flops = 2.0 * f.nnzb * 64 * Bn * Ho * Wo
         nbytes = 2 * f.nnzb * 64 + 4 * f.nnzb + 4 * (F // 64 + 1) + 4 * F + per
         row = dict(Ho=Ho, Wo=Wo, C=Cc, F=F, R=R, S=S, stride=stride, uses=uses, batch=Bn, us=t * 1e6,
@@ -132,11 +153,18 @@ def sweep_resnet50(args, sb, torch):
                    tile=ops[0]._state.tokens_per_cta)
         rows.append(row)
         total += t * uses
-        print("conv {Ho:3d}x{Wo:<3d} C={C:5d} F={F:5d} {R}x{S}/{stride} x{uses}: {us:9.1f} us  {nonzero_tflops:7.1f} nz-TFLOP/s  "
-              "roofline {roofline_frac:.3f}  tile {tile}".format(**row), flush=True)
+        if rank == 0:
+            print("conv {Ho:3d}x{Wo:<3d} C={C:5d} F={F:5d} {R}x{S}/{stride} x{uses}: {us:9.1f} us  {nonzero_tflops:7.1f} nz-TFLOP/s  "
+                  "roofline {roofline_frac:.3f}  tile {tile}".format(**row), flush=True)
         del ops, xs, os_, f
-    summary = dict(batch=Bn, chained=bool(args.chained), pruned_layers_ms=total * 1e3, images_per_s=Bn / total)
-    print("resnet50 pruned layers, batch {batch}, chained={chained}: {pruned_layers_ms:.3f} ms per forward pass -> {images_per_s:.0f} images/s".format(**summary))
+    summary = dict(batch=args.batch, gpus=world, batch_per_gpu=Bn, chained=bool(args.chained), pruned_layers_ms=total * 1e3,
+                   images_per_s=args.batch / total)
+    if rank == 0:
+        print("resnet50 pruned layers, batch {batch} over {gpus} GPU(s), chained={chained}: {pruned_layers_ms:.3f} ms per forward pass "
+              "-> {images_per_s:.0f} images/s".format(**summary), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
     return rows + [summary]
 
 
@@ -159,7 +187,7 @@ def main(argv=None):
         print("sweep: no CUDA device", file=sys.stderr)
         return 2
     rows = sweep_spmm(args, sb, torch) if args.which == "spmm" else sweep_resnet50(args, sb, torch)
-    if args.json:
+    if args.json and int(__import__("os").environ.get("RANK", "0")) == 0:
         with open(args.json, "w") as fh:
             json.dump(dict(which=args.which, hbm_gbs=args.hbm_gbs, tflops=args.tflops, rows=rows), fh, indent=1)
     return 0
