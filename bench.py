@@ -287,6 +287,7 @@ def run_ours(args):
         out["spconv"] = bench_spconv(sb, torch, pk, use_graph=not args.no_graph)
         out["reference_gpu_kernel"] = bench_reference_gpu(sb, torch, m, Bs[0], Ds[0])
         out["cpu_baseline"] = cpu_baseline_sample(m, threads=1, budget_s=12.0)
+        out["cpu_baseline"].pop("t_probe", None)
     if dist:
         dist.barrier()
         dist.destroy_process_group()
@@ -351,7 +352,10 @@ def bench_reference_gpu(sb, torch, m, Bd, Dd):
             "note": "single B/D pair (L2-warm), reference timing protocol"}
 
 
-def cpu_baseline_sample(m, threads: int, budget_s: float):
+_CPU_B_CACHE = {}
+
+
+def cpu_baseline_sample(m, threads: int, budget_s: float, t_probe: float = 0.0):
     """Times the reference's CPU check (oracle/_ref, unmodified get_host_reference; the oracle
     port if that build is absent) on a column slice of the workload sized for ~budget_s."""
     sys.path.insert(0, str(ROOT / "tests"))
@@ -362,7 +366,9 @@ def cpu_baseline_sample(m, threads: int, budget_s: float):
     indptr, indices, values = m.indptr, m.indices, m.values
 
     def run(ncols, seed):
-        B = sb.uniform_half(seed, K_ * ncols).reshape(K_, ncols)
+        B = _CPU_B_CACHE.get((seed, ncols))
+        if B is None:                        # inputs are built outside the timed part and reused
+            B = _CPU_B_CACHE[(seed, ncols)] = sb.uniform_half(seed, K_ * ncols).reshape(K_, ncols)
         t0 = time.perf_counter()
         if use_ref:
             oa.ref_spmm_host_reference(M_, K_, ncols, V_, indptr, indices, values, perm, B)
@@ -370,8 +376,9 @@ def cpu_baseline_sample(m, threads: int, budget_s: float):
             oa.spmm_ref(M_, ncols, V_, indptr, indices, values, perm, B, threads=1)
         return time.perf_counter() - t0
 
-    t_probe = run(32, 1)                     # ~0.2 s: sizes the sample
-    per_thread = max(32, int(budget_s / max(t_probe, 1e-3) * 32) // 8 * 8)
+    if t_probe <= 0.0:
+        t_probe = run(32, 1)                 # ~0.2 s for 32 columns: sizes the sample
+    per_thread = max(8, int(budget_s / max(t_probe, 1e-3) * 32) // 8 * 8)
     per_thread = min(per_thread, N_)
     times = [0.0] * threads
     def work(i):
@@ -388,7 +395,7 @@ def cpu_baseline_sample(m, threads: int, budget_s: float):
     return {"value": round(2.0 * nnz * cols / wall / 1e12, 6), "unit": UNIT, "cores": threads,
             "kind": "reference" if use_ref else "port",
             "sample": f"{cols} dense columns of the {N_}-column workload ({per_thread} per thread), {wall:.2f} s wall",
-            "seconds": round(wall, 3)}
+            "seconds": round(wall, 3), "t_probe": t_probe}
 
 
 def run_reference(args):
@@ -401,12 +408,15 @@ def run_reference(args):
     threads = os.cpu_count() or 1
     W = max(1, min(args.warmup, 1))
     steps = max(1, args.steps)
-    budget = max(0.5, min(8.0, 150.0 / (steps + W)))   # whole run within a few minutes
+    # whole run within a few minutes whatever K is (the sample is sized from a single-thread
+    # probe; all threads together run it ~2x slower)
+    budget = min(8.0, 90.0 / (steps + W))
+    probe = 0.0
     for _ in range(W):
-        cpu_baseline_sample(m, threads, budget_s=min(budget, 1.0))
+        probe = cpu_baseline_sample(m, threads, budget_s=min(budget, 1.0), t_probe=probe)["t_probe"]
     vals, secs, sample = [], [], None
     for _ in range(steps):
-        r = cpu_baseline_sample(m, threads, budget_s=budget)
+        r = cpu_baseline_sample(m, threads, budget_s=budget, t_probe=probe)
         vals.append(r["value"]); secs.append(r["seconds"]); sample = r
     value = statistics.mean(vals)
     world = int(os.environ.get("WORLD_SIZE", "1"))
