@@ -6,11 +6,20 @@
 //
 //     acc[token][m] = sum_p  G[p][token] * W[p][m]          p over the block's non-zero columns
 //
-// on the 5th-generation tensor cores.  Tokens are the UMMA M dimension (128 TMEM lanes, the
-// full-rate shape), the V rows of the block the UMMA N dimension (32/64/128 all legal),
-// K = 16 per instruction.  Both operands are MN-major in shared memory: W[p][0..V) is a
-// contiguous slice of the value panels, G[p][..] is row indices[p] of the dense operand,
-// gathered from L2.
+// on the 5th-generation tensor cores, K = 16 per instruction, both operands MN-major in shared
+// memory: W[p][0..V) is a contiguous slice of the value panels, G[p][..] is row indices[p] of
+// the dense operand, gathered from L2.  Two orientations exist (template parameter MODE):
+//   tokens in lanes  tokens are the UMMA M dimension (128 TMEM lanes), the V rows of the block
+//                    the N dimension (32/64/128): TM instructions per 16 columns.  Used for
+//                    V = 32, for SpConv writing NHWC, and for blocks with few columns.
+//   rows in lanes    the V rows are M (64 or 128 lanes; M = 64 occupies the first 16 lanes of
+//                    every 32-lane quadrant) and the T tokens N (128 or 256): ONE instruction
+//                    per 16 columns.  An MMA costs >= 73 clk whatever its N up to 128 and 133
+//                    clk at N = 256, so this halves the instruction count at ~8 % less tensor
+//                    time, and the accumulator holds one output row per lane.  Default for
+//                    SpMM and chained SpConv with V = 64 / 128 and >= 3 stages of columns.
+// The description below is written for the first orientation; the second differs in the
+// gathered tile's layout ([K group][T/64 swizzle atoms]), the MMA issue and the epilogue.
 //
 // One CTA per SM loops over items (item = blockIdx.x + i*gridDim.x); their extents are read
 // once into a shared-memory table.  Warp roles (warp w issues from scheduler partition w % 4):
