@@ -198,3 +198,14 @@ def test_both_operand_orientations(V, swap, tokens):
     assert op._state.variant == swap and op2._state.variant == swap
     assert_close_fp16(D, _oracle(m, N, B, 0.5, Cm, -1.5), what=f"V={V} swap={swap} alpha/beta")
     assert_close_fp16(D2, _oracle(m, N, B), what=f"V={V} swap={swap}")
+
+
+@pytest.mark.parametrize("N", [8, 40, 136])
+def test_rows_in_lanes_kernel_with_narrow_dense_operands(N):
+    """Forced rows-in-lanes kernel where the dense width is a fraction of one token tile."""
+    m = sb.BlockwiseSpMatrix().init_random(128, 256, 64, 1, 0.5, True, 77, values="uniform")
+    B = sb.uniform_half(78 + N, 256 * N).reshape(256, N)
+    with operand_swap(1):
+        D, op = run_spmm(m, N, B)
+    assert op._state.variant == 1
+    assert_close_fp16(D, _oracle(m, N, B), what=f"rows in lanes, N={N}")
