@@ -226,7 +226,10 @@ typedef struct shflbw_spconv_state {
 /* Replaces SpconvBlockwiseOp::initialize / SpconvBlockwiseInitFn
  * (block_sparse/spconv/blockwise_op.h:70-131, 161-167).  ifmap/ofmap are NHWC device
  * pointers.  Scratch for the staged input (and, with a filter permutation, the staged
- * output) is allocated once per (matrix, shape) and owned by the matrix handle. */
+ * output) is owned by the filter handle and shared by every state initialised from it: run
+ * those states one at a time (one stream, or ordered by events).  A later init with a larger
+ * shape allocates larger scratch; states made before stay valid (their scratch is kept until
+ * the handle is destroyed). */
 int shflbw_spconv_init(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
                        const void* ifmap_nhwc, void* ofmap_nhwc, float alpha, int kernel,
                        shflbw_spconv_state_t* out);

@@ -37,6 +37,18 @@ int ensure_buffer(void** buf, size_t* have, size_t need) {
     return SHFLBW_OK;
 }
 
+// Conv scratch grows without freeing the outgrown buffer: states initialised earlier keep
+// non-owning pointers to it.  Everything is released with the matrix's device copy.
+int grow_scratch(shflbw_matrix& m, void** buf, size_t* have, size_t need) {
+    if (*have >= need && *buf) return SHFLBW_OK;
+    void* fresh = nullptr;
+    CK(cudaMalloc(&fresh, need));
+    if (*buf) m.retired.push_back(*buf);
+    *buf = fresh;
+    *have = need;
+    return SHFLBW_OK;
+}
+
 // ---- kernel table -------------------------------------------------------------------
 using PanelKernel = void (*)(const shflbw::PanelParams);
 struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; };
@@ -144,6 +156,8 @@ namespace shflbw {
 void drop_device_copy(shflbw_matrix& m) {
     void** bufs[] = {&m.d_meta, &m.d_val, &m.stage_in, &m.stage_c, &m.stage_out, &m.conv_in, &m.conv_out};
     for (void** b : bufs) if (*b) { cudaFree(*b); *b = nullptr; }
+    for (void* r : m.retired) cudaFree(r);
+    m.retired.clear();
     m.stage_in_bytes = m.stage_c_bytes = m.stage_out_bytes = m.conv_in_bytes = m.conv_out_bytes = 0;
     m.d_kptr = m.d_kidx = m.d_perm = m.d_kcrs = nullptr;
     m.d_status = nullptr;
@@ -375,11 +389,11 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     out->shared_mem_size = ch.smem;
     // Scratch owned by the filter handle, grown on demand.
     out->staged_in_bytes = (size_t)staged_elems * 2;
-    if ((rc = ensure_buffer(&f->conv_in, &f->conv_in_bytes, out->staged_in_bytes)) != SHFLBW_OK) return rc;
+    if ((rc = grow_scratch(*f, &f->conv_in, &f->conv_in_bytes, out->staged_in_bytes)) != SHFLBW_OK) return rc;
     out->staged_in = f->conv_in;
     if (f->row_permute) {
         out->staged_out_bytes = (size_t)B * Ho * Wo * f->F * 2;
-        if ((rc = ensure_buffer(&f->conv_out, &f->conv_out_bytes, out->staged_out_bytes)) != SHFLBW_OK) return rc;
+        if ((rc = grow_scratch(*f, &f->conv_out, &f->conv_out_bytes, out->staged_out_bytes)) != SHFLBW_OK) return rc;
         out->staged_out = f->conv_out;
         if (unperm_smem_bytes(f->F) > 227 * 1024 || f->F > 65536) return SHFLBW_ERR_UNSUPPORTED;
         if (unperm_smem_bytes(f->F) > 48 * 1024)

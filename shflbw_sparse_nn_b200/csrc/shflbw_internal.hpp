@@ -66,6 +66,7 @@ struct shflbw_matrix {
     void* stage_out = nullptr; size_t stage_out_bytes = 0;   // host-call staging of D / ofmap
     void* conv_in = nullptr;   size_t conv_in_bytes = 0;     // input re-laid channel-major
     void* conv_out = nullptr;  size_t conv_out_bytes = 0;    // output in stored filter order
+    std::vector<void*> retired;    // outgrown conv scratch: op states made earlier still point at it
 };
 
 namespace shflbw {

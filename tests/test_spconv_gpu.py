@@ -119,3 +119,26 @@ def test_filter_block_height_16_runs_on_the_cuda_core_kernel():
     O, op = run_spconv(f, 4, 6, 5, 1, x)
     assert op._state.kernel == sb.KERNEL_SIMT and op.launches_per_exec == 1
     assert_close_fp16(O, _oracle(f, 4, 6, 5, 1, x), what="conv V=16")
+
+
+def test_states_stay_valid_when_a_later_init_needs_larger_scratch():
+    """The filter handle owns the conv scratch; a later, larger init must not pull it from
+    under a state made earlier."""
+    f = sb.BlockwiseSpFilter().init_random(128, 3, 3, 32, 64, 1, 0.3, True, 12, values="uniform")
+    f.transform_and_sync_device()
+    x1 = sb.uniform_half(81, 2 * 5 * 5 * 32).reshape(2, 5, 5, 32)
+    x2 = sb.uniform_half(82, 16 * 12 * 12 * 32).reshape(16, 12, 12, 32)
+    x1d, x2d = dev(x1), dev(x2)
+    o1 = torch.zeros((2, 5, 5, 128), dtype=torch.float16, device="cuda")
+    o2 = torch.zeros((16, 12, 12, 128), dtype=torch.float16, device="cuda")
+    s = torch.cuda.current_stream()
+    op1 = sb.SpconvBlockwiseOp().initialize(f, 2, 5, 5, 1, x1d, o1)
+    op1(s)
+    op2 = sb.SpconvBlockwiseOp().initialize(f, 16, 12, 12, 1, x2d, o2)    # larger: scratch grows
+    op2(s)
+    o1.zero_()
+    op1(s)                                                                 # the earlier state again
+    torch.cuda.synchronize()
+    f.device_status()
+    assert_close_fp16(host(o1), _oracle(f, 2, 5, 5, 1, x1), what="small state after growth")
+    assert_close_fp16(host(o2), _oracle(f, 16, 12, 12, 1, x2), what="large state")
