@@ -40,7 +40,7 @@ enum {
     SHFLBW_ERR_BAD_FORMAT = 2,     /* indptr/indices/perm fail validation, parse error   */
     SHFLBW_ERR_UNSUPPORTED = 3,    /* shape outside the contract (V, N % 8, C % 8, ...)  */
     SHFLBW_ERR_CUDA = 4,           /* a CUDA runtime call failed (see shflbw_last_cuda_error) */
-    SHFLBW_ERR_NOT_ON_DEVICE = 5,  /* op init before shflbw_matrix_to_device             */
+    SHFLBW_ERR_NOT_ON_DEVICE = 5,  /* no device copy, or it lives on another GPU than the current one */
     SHFLBW_ERR_DEVICE_TIMEOUT = 6, /* a bounded in-kernel wait gave up (status word set) */
     SHFLBW_ERR_IO = 7,
     SHFLBW_ERR_TOO_LARGE = 8       /* needs more than a fixed built-in capacity           */

@@ -37,6 +37,13 @@ int ensure_buffer(void** buf, size_t* have, size_t need) {
     return SHFLBW_OK;
 }
 
+// The device copy lives on the GPU that was current in shflbw_matrix_to_device; launching its
+// pointers on another GPU would fault, so ops insist on that GPU being current.
+bool on_current_device(const shflbw_matrix& m) {
+    int dev = -1;
+    return m.d_meta && cudaGetDevice(&dev) == cudaSuccess && dev == m.device;
+}
+
 // Conv scratch grows without freeing the outgrown buffer: states initialised earlier keep
 // non-owning pointers to it.  Everything is released with the matrix's device copy.
 int grow_scratch(shflbw_matrix& m, void** buf, size_t* have, size_t need) {
@@ -227,7 +234,7 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
     if (!m || !B || !D || N <= 0) return SHFLBW_ERR_INVALID_ARG;
     if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
     if (beta != 0.f && !C) return SHFLBW_ERR_INVALID_ARG;
-    if (!m->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;           // reference: assert(device_synced)
+    if (!on_current_device(*m)) return SHFLBW_ERR_NOT_ON_DEVICE;  // reference: assert(device_synced)
     if (m->bcol != 1) return SHFLBW_ERR_UNSUPPORTED;            // reference: assert(bcol == BK)
     // Row-block heights 32/64/128 run on the tensor-core kernel.  V = 16 (which the reference
     // also instantiates, spmm/blockwise_library.cu:15-31) is served by the plain CUDA-core kernel.
@@ -345,7 +352,7 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
     if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
     if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
-    if (!f->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+    if (!on_current_device(*f)) return SHFLBW_ERR_NOT_ON_DEVICE;
     if (f->brow == 16 && kernel == SHFLBW_KERNEL_AUTO) kernel = SHFLBW_KERNEL_SIMT;   // as for SpMM
     if (kernel != SHFLBW_KERNEL_SIMT && f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
     if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
@@ -510,7 +517,7 @@ int shflbw_chain_export_nhwc(const void* chain_buf, int B, int H, int W, int F, 
     const int* perm = nullptr;
     if (producer) {
         if (producer->nrow != F) return SHFLBW_ERR_BAD_FORMAT;
-        if (!producer->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+        if (!on_current_device(*producer)) return SHFLBW_ERR_NOT_ON_DEVICE;
         perm = producer->d_perm;
     }
     const size_t smem = (size_t)F * 16;
@@ -534,7 +541,7 @@ int shflbw_spconv_chain_init(shflbw_matrix_t* f, int B, int Hin, int Win, int st
     if (!f || !in_chain || !out_chain || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0 || R_next <= 0 || S_next <= 0)
         return SHFLBW_ERR_INVALID_ARG;
     if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
-    if (!f->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+    if (!on_current_device(*f)) return SHFLBW_ERR_NOT_ON_DEVICE;
     if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
     if (f->C % 8 || !f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
     if (((uintptr_t)in_chain | (uintptr_t)out_chain) & 15) return SHFLBW_ERR_UNSUPPORTED;
@@ -571,7 +578,7 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
                                       const void* ifmap, void* ofmap, float alpha, void* stream) {
     if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
     if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
-    if (!f->d_meta) return SHFLBW_ERR_NOT_ON_DEVICE;
+    if (!on_current_device(*f)) return SHFLBW_ERR_NOT_ON_DEVICE;
     if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
     if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
     if (((uintptr_t)ifmap | (uintptr_t)ofmap) & 15) return SHFLBW_ERR_UNSUPPORTED;
