@@ -11,7 +11,10 @@ from .blockwise import (BlockwiseSpFilter, BlockwiseSpMatrix, SpconvBlockwiseExe
                         SpconvBlockwiseInitFn, SpconvBlockwiseOp, SpmmBlockwiseExecFn,
                         SpmmBlockwiseInitFn, SpmmBlockwiseOp, spconv_host, spmm_host, uniform_half)
 
+from .pruner import prune_conv_filter, prune_matrix
+
 __all__ = [
+    "prune_matrix", "prune_conv_filter",
     "BlockwiseSpMatrix", "BlockwiseSpFilter", "SpmmBlockwiseOp", "SpmmBlockwiseInitFn",
     "SpmmBlockwiseExecFn", "SpconvBlockwiseOp", "SpconvBlockwiseInitFn", "SpconvBlockwiseExecFn",
     "spmm_host", "spconv_host", "uniform_half", "ShflbwError",
