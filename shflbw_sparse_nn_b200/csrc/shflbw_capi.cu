@@ -165,6 +165,8 @@ void drop_device_copy(shflbw_matrix& m) {
     for (void** b : bufs) if (*b) { cudaFree(*b); *b = nullptr; }
     for (void* r : m.retired) cudaFree(r);
     m.retired.clear();
+    for (void*& st : m.host_streams) if (st) { cudaStreamDestroy((cudaStream_t)st); st = nullptr; }
+    for (void*& ev : m.host_events) if (ev) { cudaEventDestroy((cudaEvent_t)ev); ev = nullptr; }
     m.stage_in_bytes = m.stage_c_bytes = m.stage_out_bytes = m.conv_in_bytes = m.conv_out_bytes = 0;
     m.d_kptr = m.d_kidx = m.d_perm = m.d_kcrs = nullptr;
     m.d_status = nullptr;
@@ -306,25 +308,80 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
 
 int shflbw_spmm_launches_per_exec(const shflbw_spmm_state_t* st) { return st && st->init_success ? 1 : 0; }
 
+// Host-buffer SpMM.  The dense operand is cut into column chunks that move through three
+// streams -- host-to-device copy of chunk i+1, kernel on chunk i, device-to-host copy of chunk
+// i-1 -- so that on a full-duplex link the call costs about the larger of the two transfers
+// instead of their sum plus the kernel.  (Overlap needs page-locked host buffers; pageable ones
+// work, the copies then serialise.)  A chunk is staged contiguously ([K][w] / [M][w]) by a strided
+// 2-D copy, so the kernels run unchanged on dense chunks.
 int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha, const void* C_host,
                      float beta, void* D_host) {
     if (!m || !B_host || !D_host || N <= 0) return SHFLBW_ERR_INVALID_ARG;
     if (beta != 0.f && !C_host) return SHFLBW_ERR_INVALID_ARG;
+    if (N % 8) return SHFLBW_ERR_UNSUPPORTED;
     int rc = shflbw_matrix_to_device(m);
     if (rc != SHFLBW_OK) return rc;
     const size_t bB = (size_t)m->ncol * N * 2, bD = (size_t)m->nrow * N * 2;
     if ((rc = ensure_buffer(&m->stage_in, &m->stage_in_bytes, bB)) != SHFLBW_OK) return rc;
     if ((rc = ensure_buffer(&m->stage_out, &m->stage_out_bytes, bD)) != SHFLBW_OK) return rc;
     if (beta != 0.f && (rc = ensure_buffer(&m->stage_c, &m->stage_c_bytes, bD)) != SHFLBW_OK) return rc;
-    CK(cudaMemcpyAsync(m->stage_in, B_host, bB, cudaMemcpyHostToDevice, 0));
-    if (beta != 0.f) CK(cudaMemcpyAsync(m->stage_c, C_host, bD, cudaMemcpyHostToDevice, 0));
-    shflbw_spmm_state_t st;
-    rc = shflbw_spmm_init(m, N, m->stage_in, alpha, beta != 0.f ? m->stage_c : nullptr, beta, m->stage_out,
-                          SHFLBW_KERNEL_AUTO, &st);
-    if (rc != SHFLBW_OK) return rc;
-    if ((rc = shflbw_spmm_exec(&st, 0)) != SHFLBW_OK) return rc;
-    CK(cudaMemcpyAsync(D_host, m->stage_out, bD, cudaMemcpyDeviceToHost, 0));
-    CK(cudaStreamSynchronize(0));
+
+    // chunk width: a quarter of N rounded up to whole 256-token tiles; narrow operands go in one piece
+    int w = N;
+    int want = 4;
+    if (const char* e = getenv("SHFLBW_HOST_CHUNKS")) want = atoi(e) > 0 && atoi(e) <= 8 ? atoi(e) : 4;
+    if (N >= 2048 && want > 1) w = ((N + want - 1) / want + 255) / 256 * 256;
+    const int chunks = (N + w - 1) / w;
+    constexpr int kMaxChunks = 8;
+    if (chunks > kMaxChunks) return SHFLBW_ERR_UNSUPPORTED;   // cannot happen: w >= N/4
+
+    // streams and events live in the handle (creating and destroying them costs more than the
+    // overlap gains on a call of about a millisecond)
+    auto fail = [&](int code) { cudaDeviceSynchronize(); return code; };
+#define CKH(call) do { if (!cuda_ok((call), #call)) return fail(SHFLBW_ERR_CUDA); } while (0)
+    if (!m->host_streams[0]) {
+        for (int i = 0; i < 3; ++i) {
+            cudaStream_t st_ = nullptr;
+            CKH(cudaStreamCreateWithFlags(&st_, cudaStreamNonBlocking));
+            m->host_streams[i] = st_;
+        }
+        for (int i = 0; i < 2 * kMaxChunks; ++i) {
+            cudaEvent_t ev_ = nullptr;
+            CKH(cudaEventCreateWithFlags(&ev_, cudaEventDisableTiming));
+            m->host_events[i] = ev_;
+        }
+    }
+    cudaStream_t s_in = (cudaStream_t)m->host_streams[0], s_k = (cudaStream_t)m->host_streams[1],
+                 s_out = (cudaStream_t)m->host_streams[2];
+    cudaEvent_t* e_in = (cudaEvent_t*)&m->host_events[0];
+    cudaEvent_t* e_k = (cudaEvent_t*)&m->host_events[kMaxChunks];
+    const size_t pitch_h = (size_t)N * 2;
+    for (int i = 0; i < chunks; ++i) {
+        const int c0 = i * w, wi = (N - c0 < w) ? N - c0 : w;
+        // chunk i of the staging buffers: contiguous [rows][wi] blocks, one after the other
+        __half* dB = (__half*)m->stage_in + (size_t)m->ncol * c0;
+        __half* dD = (__half*)m->stage_out + (size_t)m->nrow * c0;
+        __half* dC = beta != 0.f ? (__half*)m->stage_c + (size_t)m->nrow * c0 : nullptr;
+        CKH(cudaMemcpy2DAsync(dB, (size_t)wi * 2, (const __half*)B_host + c0, pitch_h, (size_t)wi * 2, m->ncol,
+                              cudaMemcpyHostToDevice, s_in));
+        if (dC)
+            CKH(cudaMemcpy2DAsync(dC, (size_t)wi * 2, (const __half*)C_host + c0, pitch_h, (size_t)wi * 2, m->nrow,
+                                  cudaMemcpyHostToDevice, s_in));
+        CKH(cudaEventRecord(e_in[i], s_in));
+        CKH(cudaStreamWaitEvent(s_k, e_in[i], 0));
+        shflbw_spmm_state_t st;
+        rc = shflbw_spmm_init(m, wi, dB, alpha, dC, beta, dD, SHFLBW_KERNEL_AUTO, &st);
+        if (rc == SHFLBW_OK) rc = shflbw_spmm_exec(&st, s_k);
+        if (rc != SHFLBW_OK) return fail(rc);
+        CKH(cudaEventRecord(e_k[i], s_k));
+        CKH(cudaStreamWaitEvent(s_out, e_k[i], 0));
+        CKH(cudaMemcpy2DAsync((__half*)D_host + c0, pitch_h, dD, (size_t)wi * 2, (size_t)wi * 2, m->nrow,
+                              cudaMemcpyDeviceToHost, s_out));
+    }
+    CKH(cudaStreamSynchronize(s_out));
+    CKH(cudaStreamSynchronize(s_k));
+    CKH(cudaStreamSynchronize(s_in));
+#undef CKH
     return SHFLBW_OK;
 }
 

@@ -67,6 +67,9 @@ struct shflbw_matrix {
     void* conv_in = nullptr;   size_t conv_in_bytes = 0;     // input re-laid channel-major
     void* conv_out = nullptr;  size_t conv_out_bytes = 0;    // output in stored filter order
     std::vector<void*> retired;    // outgrown conv scratch: op states made earlier still point at it
+    // streams (copy in, kernels, copy out) and events of the pipelined host-buffer call, made on first use
+    void* host_streams[3] = {nullptr, nullptr, nullptr};
+    void* host_events[16] = {};
 };
 
 namespace shflbw {

@@ -209,3 +209,19 @@ def test_rows_in_lanes_kernel_with_narrow_dense_operands(N):
         D, op = run_spmm(m, N, B)
     assert op._state.variant == 1
     assert_close_fp16(D, _oracle(m, N, B), what=f"rows in lanes, N={N}")
+
+
+def test_host_buffer_call_pipelines_wide_operands_in_column_chunks():
+    """N >= 2048: the host-buffer call cuts the dense operand into column chunks (copy in, kernel
+    and copy out overlap); ragged last chunk, alpha and beta * C included."""
+    M, K, N = 256, 320, 2056                      # chunks of 768, 768 and 520 columns
+    m = sb.BlockwiseSpMatrix().init_random(M, K, 64, 1, 0.3, True, 31, values="uniform")
+    B = sb.uniform_half(32, K * N).reshape(K, N)
+    Cm = sb.uniform_half(33, M * N).reshape(M, N)
+    D_host = np.full((M, N), np.float16(7), np.float16)
+    sb.spmm_host(m, N, B, D_host, alpha=0.5, C_host=Cm, beta=2.0)
+    m.device_status()
+    assert_close_fp16(D_host, _oracle(m, N, B, 0.5, Cm, 2.0), what="chunked host call")
+    D_dev, _ = run_spmm(m, N, B, alpha=0.5, Cm=Cm, beta=2.0)
+    # same kernels on the same columns: only the summation order of a token tile's partners differs -> none
+    assert_close_fp16(D_host, D_dev.astype(np.float32), what="chunked host call vs device call")
