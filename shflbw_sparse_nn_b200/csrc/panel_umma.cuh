@@ -60,7 +60,7 @@ struct PanelParams {
     // sparse operand (kernel image)
     const int* blk_ptr;      // [X+1] padded offsets (multiples of 16)
     const int* blk_idx;      // padded column ids
-    const __half* blk_val;   // [rows][V]
+    const __half* blk_val;   // value panels of the padded rows, element order kval_index() (shflbw_internal.hpp)
     const int* perm;         // [M] or nullptr
     int* status_word;
     float alpha, beta;
