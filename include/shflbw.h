@@ -186,8 +186,11 @@ int shflbw_matrix_device_status(const shflbw_matrix_t* m);
 
 /* End-to-end call with HOST buffers (what a plugin caller without device memory uses):
  * copies B (and C) to the device, runs, copies D back, synchronises.  B/C/D are host
- * pointers (pinned memory recommended).  Reuses device staging buffers owned by the matrix
- * handle across calls. */
+ * pointers.  Operands of 2048 columns or more move in four column chunks through three
+ * streams (copy in, kernels, copy out) so that the two transfers overlap; that needs
+ * page-locked host memory (pageable buffers work, without the overlap).  Device staging
+ * buffers, streams and events are owned by the matrix handle and reused across calls: one
+ * host-buffer call per handle at a time. */
 int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
                      const void* C_host, float beta, void* D_host);
 
