@@ -241,7 +241,10 @@ int shflbw_spconv_init(shflbw_matrix_t* filter, int B, int Hin, int Win, int str
  * (block_sparse/spconv/blockwise_op.h:148-153, 177-187). */
 int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream);
 
-/* End-to-end conv with HOST NHWC buffers. */
+/* End-to-end conv with HOST NHWC buffers.  Batches of 32 images or more move in up to four
+ * chunks of whole 8-image groups through the same three streams as shflbw_spmm_host (copy in,
+ * kernels, copy out overlap; page-locked host memory needed for the overlap).  One host-buffer
+ * call per handle at a time. */
 int shflbw_spconv_host(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
                        const void* ifmap_host, void* ofmap_host, float alpha);
 

@@ -56,6 +56,27 @@ int grow_scratch(shflbw_matrix& m, void** buf, size_t* have, size_t need) {
     return SHFLBW_OK;
 }
 
+// Streams and events of the pipelined host-buffer calls, owned by the handle (made on first use).
+int host_pipeline(shflbw_matrix* m, cudaStream_t* s_in, cudaStream_t* s_k, cudaStream_t* s_out,
+                         cudaEvent_t** e_in, cudaEvent_t** e_k) {
+    if (!m->host_streams[0]) {
+        for (int i = 0; i < 3; ++i) {
+            cudaStream_t st_ = nullptr;
+            CK(cudaStreamCreateWithFlags(&st_, cudaStreamNonBlocking));
+            m->host_streams[i] = st_;
+        }
+        for (int i = 0; i < 16; ++i) {
+            cudaEvent_t ev_ = nullptr;
+            CK(cudaEventCreateWithFlags(&ev_, cudaEventDisableTiming));
+            m->host_events[i] = ev_;
+        }
+    }
+    *s_in = (cudaStream_t)m->host_streams[0]; *s_k = (cudaStream_t)m->host_streams[1];
+    *s_out = (cudaStream_t)m->host_streams[2];
+    *e_in = (cudaEvent_t*)&m->host_events[0]; *e_k = (cudaEvent_t*)&m->host_events[8];
+    return SHFLBW_OK;
+}
+
 // ---- kernel table -------------------------------------------------------------------
 using PanelKernel = void (*)(const shflbw::PanelParams);
 struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; };
@@ -339,22 +360,9 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
     // overlap gains on a call of about a millisecond)
     auto fail = [&](int code) { cudaDeviceSynchronize(); return code; };
 #define CKH(call) do { if (!cuda_ok((call), #call)) return fail(SHFLBW_ERR_CUDA); } while (0)
-    if (!m->host_streams[0]) {
-        for (int i = 0; i < 3; ++i) {
-            cudaStream_t st_ = nullptr;
-            CKH(cudaStreamCreateWithFlags(&st_, cudaStreamNonBlocking));
-            m->host_streams[i] = st_;
-        }
-        for (int i = 0; i < 2 * kMaxChunks; ++i) {
-            cudaEvent_t ev_ = nullptr;
-            CKH(cudaEventCreateWithFlags(&ev_, cudaEventDisableTiming));
-            m->host_events[i] = ev_;
-        }
-    }
-    cudaStream_t s_in = (cudaStream_t)m->host_streams[0], s_k = (cudaStream_t)m->host_streams[1],
-                 s_out = (cudaStream_t)m->host_streams[2];
-    cudaEvent_t* e_in = (cudaEvent_t*)&m->host_events[0];
-    cudaEvent_t* e_k = (cudaEvent_t*)&m->host_events[kMaxChunks];
+    cudaStream_t s_in, s_k, s_out;
+    cudaEvent_t *e_in, *e_k;
+    if ((rc = host_pipeline(m, &s_in, &s_k, &s_out, &e_in, &e_k)) != SHFLBW_OK) return rc;
     const size_t pitch_h = (size_t)N * 2;
     for (int i = 0; i < chunks; ++i) {
         const int c0 = i * w, wi = (N - c0 < w) ? N - c0 : w;
@@ -529,6 +537,9 @@ int shflbw_spconv_launches_per_exec(const shflbw_spconv_state_t* st) {
     return st->staged_out ? 3 : 2;
 }
 
+// Host-buffer SpConv.  Batches of 32 images or more go in up to four chunks of whole 8-image
+// groups (NHWC: a batch slice is contiguous on both sides) through the same three streams as
+// the SpMM host call, so that copy in, kernels and copy out overlap.
 int shflbw_spconv_host(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap_host,
                        void* ofmap_host, float alpha) {
     if (!f || !ifmap_host || !ofmap_host || !f->is_filter || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0)
@@ -536,20 +547,41 @@ int shflbw_spconv_host(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     int rc = shflbw_matrix_to_device(f);
     if (rc != SHFLBW_OK) return rc;
     const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
-    const size_t bI = (size_t)B * Hin * Win * f->C * 2, bO = (size_t)B * Ho * Wo * f->F * 2;
-    if ((rc = ensure_buffer(&f->stage_in, &f->stage_in_bytes, bI)) != SHFLBW_OK) return rc;
-    if ((rc = ensure_buffer(&f->stage_out, &f->stage_out_bytes, bO)) != SHFLBW_OK) return rc;
-    CK(cudaMemcpyAsync(f->stage_in, ifmap_host, bI, cudaMemcpyHostToDevice, 0));
-    shflbw_spconv_state_t st;
-    rc = shflbw_spconv_init(f, B, Hin, Win, stride, f->stage_in, f->stage_out, alpha, SHFLBW_KERNEL_AUTO, &st);
-    if (rc != SHFLBW_OK) return rc;
-    if ((rc = shflbw_spconv_exec(&st, 0)) != SHFLBW_OK) return rc;
-    CK(cudaMemcpyAsync(ofmap_host, f->stage_out, bO, cudaMemcpyDeviceToHost, 0));
-    CK(cudaStreamSynchronize(0));
+    const size_t img_in = (size_t)Hin * Win * f->C, img_out = (size_t)Ho * Wo * f->F;   // elements per image
+    if ((rc = ensure_buffer(&f->stage_in, &f->stage_in_bytes, (size_t)B * img_in * 2)) != SHFLBW_OK) return rc;
+    if ((rc = ensure_buffer(&f->stage_out, &f->stage_out_bytes, (size_t)B * img_out * 2)) != SHFLBW_OK) return rc;
+    int per = B;                                     // images per chunk
+    if (B >= 32) per = ((B + 3) / 4 + 7) / 8 * 8;
+    const int chunks = (B + per - 1) / per;          // <= 4
+    cudaStream_t s_in, s_k, s_out;
+    cudaEvent_t *e_in, *e_k;
+    if ((rc = host_pipeline(f, &s_in, &s_k, &s_out, &e_in, &e_k)) != SHFLBW_OK) return rc;
+    auto fail = [&](int code) { cudaDeviceSynchronize(); return code; };
+#define CKH(call) do { if (!cuda_ok((call), #call)) return fail(SHFLBW_ERR_CUDA); } while (0)
+    for (int i = 0; i < chunks; ++i) {
+        const int b0 = i * per, nb = (B - b0 < per) ? B - b0 : per;
+        __half* dI = (__half*)f->stage_in + (size_t)b0 * img_in;
+        __half* dO = (__half*)f->stage_out + (size_t)b0 * img_out;
+        CKH(cudaMemcpyAsync(dI, (const __half*)ifmap_host + (size_t)b0 * img_in, (size_t)nb * img_in * 2,
+                            cudaMemcpyHostToDevice, s_in));
+        CKH(cudaEventRecord(e_in[i], s_in));
+        CKH(cudaStreamWaitEvent(s_k, e_in[i], 0));
+        shflbw_spconv_state_t st;
+        rc = shflbw_spconv_init(f, nb, Hin, Win, stride, dI, dO, alpha, SHFLBW_KERNEL_AUTO, &st);
+        if (rc == SHFLBW_OK) rc = shflbw_spconv_exec(&st, s_k);
+        if (rc != SHFLBW_OK) return fail(rc);
+        CKH(cudaEventRecord(e_k[i], s_k));
+        CKH(cudaStreamWaitEvent(s_out, e_k[i], 0));
+        CKH(cudaMemcpyAsync((__half*)ofmap_host + (size_t)b0 * img_out, dO, (size_t)nb * img_out * 2,
+                            cudaMemcpyDeviceToHost, s_out));
+    }
+    CKH(cudaStreamSynchronize(s_out));
+    CKH(cudaStreamSynchronize(s_k));
+    CKH(cudaStreamSynchronize(s_in));
+#undef CKH
     return SHFLBW_OK;
 }
 
-// SpConv without any allocation: scratch lives in g_static_scratch (see shflbw.h).
 // ---- chained layers ---------------------------------------------------------------------
 
 size_t shflbw_chain_buffer_elems(int C, int H, int W, int B, int R, int S) {

@@ -142,3 +142,15 @@ def test_states_stay_valid_when_a_later_init_needs_larger_scratch():
     f.device_status()
     assert_close_fp16(host(o1), _oracle(f, 2, 5, 5, 1, x1), what="small state after growth")
     assert_close_fp16(host(o2), _oracle(f, 16, 12, 12, 1, x2), what="large state")
+
+
+def test_host_buffer_call_pipelines_large_batches_in_chunks():
+    """B >= 32: the host-buffer call splits the batch into chunks of whole 8-image groups
+    (here 16 + 16 + 8) whose copies and kernels overlap."""
+    Bn, H, W, Cc, F = 40, 6, 5, 32, 128
+    f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, 64, 1, 0.3, True, 19, values="uniform")
+    x = sb.uniform_half(91, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    out = np.full((Bn, H, W, F), np.float16(7), np.float16)
+    sb.spconv_host(f, Bn, H, W, 1, x, out, alpha=0.5)
+    f.device_status()
+    assert_close_fp16(out, _oracle(f, Bn, H, W, 1, x, 0.5), what="chunked host conv")
