@@ -224,6 +224,8 @@ typedef struct shflbw_spconv_state {
     int chain;               /* 1: input and output are chain buffers                   */
     int out_R, out_S;        /* filter shape of the consumer the output halo is for     */
     int relu;                /* 1: max(x, 0) fused into the epilogue                    */
+    const void* residual;    /* chained: optional residual chain buffer (output geometry) */
+    const int* residual_map; /* chained: stored filter -> plane of `residual`, or NULL     */
 } shflbw_spconv_state_t;
 
 /* Replaces SpconvBlockwiseOp::initialize / SpconvBlockwiseInitFn
@@ -282,6 +284,18 @@ int shflbw_filter_fold_input_order(const shflbw_matrix_t* filter, const shflbw_m
 int shflbw_spconv_chain_init(shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
                              const void* in_chain, void* out_chain, int R_next, int S_next,
                              float alpha, int relu, shflbw_spconv_state_t* out);
+
+/* Residual connection of a chained layer: out = relu?(alpha * conv + residual), in fp16.
+ * `res_chain` is a chain buffer with the geometry of the layer's OUTPUT (same H, W, batch and
+ * halo as out_chain); its plane map_host[f] is added to stored filter f (map_host == NULL: plane
+ * f).  shflbw_chain_residual_map fills the map for the usual case -- the residual was written
+ * by `residual_producer` (NULL: it holds logical channel order) and must meet the logical
+ * channels of `layer`'s stored filters.  Call between shflbw_spconv_chain_init and the first
+ * shflbw_spconv_exec; the device copy of the map belongs to the filter handle. */
+int shflbw_chain_residual_map(const shflbw_matrix_t* layer, const shflbw_matrix_t* residual_producer,
+                              int* map_host /* layer->F ints */);
+int shflbw_spconv_chain_set_residual(shflbw_matrix_t* filter, shflbw_spconv_state_t* st, const void* res_chain,
+                                     const int* map_host);
 
 /* SpConv for callers that must not allocate.  No counterpart in the reference project.
  *

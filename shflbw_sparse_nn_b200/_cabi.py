@@ -55,6 +55,7 @@ class SpconvState(C.Structure):
         ("blk_ptr", C.c_void_p), ("blk_idx", C.c_void_p), ("blk_val", C.c_void_p),
         ("perm", C.c_void_p), ("status_word", C.c_void_p),
         ("chain", C.c_int), ("out_R", C.c_int), ("out_S", C.c_int), ("relu", C.c_int),
+        ("residual", C.c_void_p), ("residual_map", C.c_void_p),
     ]
 
 
@@ -108,6 +109,8 @@ _PROTOS = {
     "shflbw_filter_fold_input_order": (C.c_int, [_H, _H, C.POINTER(_H)]),
     "shflbw_spconv_chain_init": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                            C.c_int, C.c_int, C.c_float, C.c_int, C.POINTER(SpconvState)]),
+    "shflbw_chain_residual_map": (C.c_int, [_H, _H, C.c_void_p]),
+    "shflbw_spconv_chain_set_residual": (C.c_int, [_H, C.POINTER(SpconvState), C.c_void_p, C.c_void_p]),
     "shflbw_spconv_exec_static_scratch": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                     C.c_float, C.c_void_p]),
 }

@@ -328,6 +328,21 @@ class SpconvChainOp:
         self._keep = (spfilter, in_chain, out_chain)
         return self
 
+    def set_residual(self, res_chain, residual_producer="same"):
+        """out = relu?(alpha * conv + residual).  `res_chain` has the output's geometry; its channel
+        order is that of `residual_producer`'s stored filters (None: logical order; "same": plane f
+        is added to stored filter f)."""
+        spfilter = self._keep[0]
+        mp = None
+        if residual_producer != "same":
+            mp = np.empty(spfilter.nrow, np.int32)
+            check(_cabi.lib().shflbw_chain_residual_map(spfilter._h, None if residual_producer is None
+                                                        else residual_producer._h, mp.ctypes.data), "chain_residual_map")
+        check(_cabi.lib().shflbw_spconv_chain_set_residual(spfilter._h, C.byref(self._state), _ptr(res_chain),
+                                                           None if mp is None else mp.ctypes.data), "set_residual")
+        self._keep = self._keep + (res_chain,)
+        return self
+
     def __call__(self, stream=None):
         check(_cabi.lib().shflbw_spconv_exec(C.byref(self._state), _stream_ptr(stream)), "SpconvChainOp()")
 

@@ -79,6 +79,8 @@ struct PanelParams {
     int Bn, Bp, Hp, Wp, Cin, F, R, S, stride, Ho, Wo;
     // chained SpConv: out[f][OHp][OWp][Bp] with the next layer's halo (origin at (oph, opw))
     int OWp, oph, opw, out_plane, relu;
+    const __half* res;       // optional residual in the OUTPUT's geometry ([planes][OHp][OWp][Bp]) or nullptr
+    const int* res_map;      // stored filter -> plane of `res` (nullptr: same index)
 };
 
 // MODE: 0 = SpMM, 1 = SpConv writing NHWC (stored filter order), 2 = SpConv writing the
@@ -546,6 +548,13 @@ panel_umma_kernel(const PanelParams p) {
                 uint32_t roff[LR / 8];                                   // D offsets of rows 8i + lane/4
 #pragma unroll
                 for (int i = 0; i < LR / 8; ++i) roff[i] = __shfl_sync(0xffffffffu, my_roff, i * 8 + (lane >> 2));
+                uint32_t rres[LR / 8];                                   // chained: residual offsets of those rows
+                const bool use_res = CHAIN && p.res != nullptr;
+                if (use_res) {
+                    const uint32_t mine = (uint32_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (uint32_t)p.out_plane;
+#pragma unroll
+                    for (int i = 0; i < LR / 8; ++i) rres[i] = __shfl_sync(0xffffffffu, mine, i * 8 + (lane >> 2));
+                }
                 const bool use_c = !CHAIN && p.beta != 0.0f && p.C != nullptr;
 #pragma unroll 1
                 for (int cc = 0; cc < HC; cc += 32) {
@@ -573,7 +582,6 @@ panel_umma_kernel(const PanelParams p) {
                                 // same arithmetic as the reference: round to fp16, then alpha in fp16
                                 h[e] = __floats2half2_rn(__uint_as_float(r[c * 8 + 2 * e]), __uint_as_float(r[c * 8 + 2 * e + 1]));
                                 if (!use_c) h[e] = __hmul2(h[e], alpha2);
-                                if (CHAIN && p.relu) h[e] = __hmax2(h[e], zero2);
                             }
                             *(uint4*)(tile + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = v;
                         }
@@ -602,6 +610,19 @@ panel_umma_kernel(const PanelParams p) {
                                     const __half* ch = (const __half*)&cv;
 #pragma unroll
                                     for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
+                                }
+                                if constexpr (CHAIN) {   // out = relu(alpha * conv + residual), fp16
+                                    __half2* h = (__half2*)&v;
+                                    if (use_res) {
+                                        const uint4 rv = *(const uint4*)(p.res + (size_t)rres[i] + (size_t)goff);
+                                        const __half2* rh = (const __half2*)&rv;
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], rh[e]);
+                                    }
+                                    if (p.relu) {
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) h[e] = __hmax2(h[e], zero2);
+                                    }
                                 }
                                 *(uint4*)(obase + off) = v;
                             }
@@ -656,10 +677,11 @@ panel_umma_kernel(const PanelParams p) {
                     goff = (uint32_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
                 }
             }
-            const __half zero1 = __float2half_rn(0.f);
+            const __half2 zero2 = __float2half2_rn(0.f);
 #pragma unroll 1
             for (int cc = 0; cc < COLS; cc += 32) {
                 uint32_t roff[4];                                        // D offsets of rows cc + 8i + lane/4
+                uint32_t rres[4] = {0u, 0u, 0u, 0u};                     // chained: residual offsets of those rows
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int m = mbase + cc + 8 * i + (lane >> 2);
@@ -668,6 +690,7 @@ panel_umma_kernel(const PanelParams p) {
                         roff[i] = (uint32_t)row * (uint32_t)p.N;
                     } else {
                         roff[i] = (uint32_t)(blk * V + m) * (uint32_t)p.out_plane;   // stored filter order
+                        if (p.res) rres[i] = (uint32_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (uint32_t)p.out_plane;
                     }
                 }
                 {
@@ -691,7 +714,6 @@ panel_umma_kernel(const PanelParams p) {
                     for (int e = 0; e < 32; ++e) {
                         __half h = __float2half_rn(__uint_as_float(r[e]));
                         if (!use_c) h = __hmul(h, alpha1);
-                        if (MODE == kPanelConvChain && p.relu) h = __hmax(h, zero1);
                         my_tile[e * 32 + lane] = h;
                     }
                 }
@@ -708,6 +730,19 @@ panel_umma_kernel(const PanelParams p) {
                                 const __half* ch = (const __half*)&cv;
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
+                            }
+                            if constexpr (MODE == kPanelConvChain) {   // out = relu(alpha * conv + residual), fp16
+                                __half2* h = (__half2*)&v;
+                                if (p.res) {
+                                    const uint4 rv = *(const uint4*)(p.res + (size_t)rres[i] + (size_t)goff);
+                                    const __half2* rh = (const __half2*)&rv;
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], rh[e]);
+                                }
+                                if (p.relu) {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) h[e] = __hmax2(h[e], zero2);
+                                }
                             }
                             *(uint4*)(obase + off) = v;
                         }

@@ -506,6 +506,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     p.Xs = (const __half*)(st->chain ? st->ifmap : st->staged_in);
     p.out = (__half*)(st->staged_out ? st->staged_out : st->ofmap);
     if (st->chain) {
+        p.res = (const __half*)st->residual; p.res_map = st->residual_map;
         const int OHp = st->Ho + st->out_R - 1;
         p.OWp = st->Wo + st->out_S - 1; p.oph = st->out_R / 2; p.opw = st->out_S / 2;
         p.out_plane = OHp * p.OWp * st->Bp; p.relu = st->relu;
@@ -660,6 +661,35 @@ int shflbw_spconv_chain_init(shflbw_matrix_t* f, int B, int Hin, int Win, int st
     out->grid_x = persistent_grid(out->num_items, sms); out->grid_y = 1;
     out->shared_mem_size = ch.smem;
     out->init_success = 1;
+    return SHFLBW_OK;
+}
+
+int shflbw_chain_residual_map(const shflbw_matrix_t* layer, const shflbw_matrix_t* producer, int* map_host) {
+    if (!layer || !map_host) return SHFLBW_ERR_INVALID_ARG;
+    const int F = layer->nrow;
+    if (producer && producer->nrow != F) return SHFLBW_ERR_BAD_FORMAT;
+    std::vector<int> where(F);      // logical channel -> plane of the residual buffer
+    for (int p = 0; p < F; ++p) where[producer && producer->row_permute ? producer->row_permute_ids[p] : p] = p;
+    for (int f = 0; f < F; ++f) map_host[f] = where[layer->row_permute ? layer->row_permute_ids[f] : f];
+    return SHFLBW_OK;
+}
+
+int shflbw_spconv_chain_set_residual(shflbw_matrix_t* f, shflbw_spconv_state_t* st, const void* res_chain,
+                                     const int* map_host) {
+    if (!f || !st || !st->init_success || !st->chain || !res_chain) return SHFLBW_ERR_INVALID_ARG;
+    if (!on_current_device(*f) || st->blk_ptr != f->d_kptr) return SHFLBW_ERR_INVALID_ARG;
+    if ((uintptr_t)res_chain & 15) return SHFLBW_ERR_UNSUPPORTED;
+    st->residual = res_chain;
+    st->residual_map = nullptr;
+    if (map_host) {
+        for (int i = 0; i < st->F; ++i)
+            if (map_host[i] < 0 || map_host[i] >= st->F) return SHFLBW_ERR_BAD_FORMAT;
+        void* d = nullptr;
+        CK(cudaMalloc(&d, (size_t)st->F * sizeof(int)));
+        f->retired.push_back(d);                       // lives as long as the filter's device copy
+        CK(cudaMemcpy(d, map_host, (size_t)st->F * sizeof(int), cudaMemcpyHostToDevice));
+        st->residual_map = (const int*)d;
+    }
     return SHFLBW_OK;
 }
 

@@ -74,3 +74,41 @@ def test_two_chained_layers_match_oracle_and_unchained_path(stride2):
     got = host(y)
     assert_close_fp16(got, ref, what=f"chained 2 layers (stride {stride2}) vs oracle")
     assert_close_fp16(got, y2_unchained.astype(np.float32), what="chained vs unchained GPU path")
+
+
+@pytest.mark.parametrize("swap", [0, 1])
+def test_residual_add_across_two_chained_layers(swap):
+    """y = relu(conv2(relu(conv1(x))) + x): an identity shortcut around two chained layers.  x is
+    imported in logical channel order, conv2's output is in conv2's stored filter order, so the
+    residual planes are picked through the map of shflbw_chain_residual_map."""
+    Bn, H, W, Cc, V = 6, 9, 8, 64, 64
+    f1 = sb.BlockwiseSpFilter().init_random(128, 1, 1, Cc, V, 1, 0.5, True, 41, values="uniform")
+    f2 = sb.BlockwiseSpFilter().init_random(Cc, 3, 3, 128, V, 1, 0.25, True, 42, values="uniform")
+    f2c = f2.fold_input_order(f1)
+    x = sb.uniform_half(43, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    # unchained reference on the GPU path + numpy for the elementwise part
+    y1, _ = run_spconv(f1, Bn, H, W, 1, x, alpha=0.25)
+    y1 = np.maximum(y1, np.float16(0))
+    y2, _ = run_spconv(f2, Bn, H, W, 1, y1, alpha=0.25)
+    want = np.maximum((y2 + x).astype(np.float16), np.float16(0))
+    want_oracle = np.maximum(oa.spconv_ref_nhwc(Bn, H, W, 128, Cc, 3, 3, 1, V, f2.indptr, f2.indices, f2.values,
+                                                f2.row_permute_ids, y1, 0.25).astype(np.float32)
+                             + x.astype(np.float32), 0)
+    s = torch.cuda.current_stream()
+    f2c.transform_and_sync_device()
+    b0 = _chain_buf(Cc, H, W, Bn, 1, 1)           # x for conv1 (1x1: no halo) -- also the residual (same geometry as y)
+    b1 = _chain_buf(128, H, W, Bn, 3, 3)
+    b2 = _chain_buf(Cc, H, W, Bn, 1, 1)
+    y = torch.full((Bn, H, W, Cc), float("nan"), dtype=torch.float16, device="cuda")
+    sb.chain_import_nhwc(dev(x), Bn, H, W, Cc, 1, 1, b0, s)
+    with operand_swap(swap):
+        l1 = sb.SpconvChainOp().initialize(f1, Bn, H, W, 1, b0, b1, 3, 3, alpha=0.25, relu=True)
+        l2 = sb.SpconvChainOp().initialize(f2c, Bn, H, W, 1, b1, b2, 1, 1, alpha=0.25, relu=True)
+    l2.set_residual(b0, residual_producer=None)    # b0 holds logical channel order
+    l1(s); l2(s)
+    sb.chain_export_nhwc(b2, Bn, H, W, Cc, 1, 1, f2c, y, s)
+    torch.cuda.synchronize()
+    f1.device_status(); f2c.device_status()
+    got = host(y)
+    assert_close_fp16(got, want_oracle, what=f"residual block vs oracle (swap {swap})")
+    assert_close_fp16(got, want.astype(np.float32), what=f"residual block vs unchained GPU path (swap {swap})")
