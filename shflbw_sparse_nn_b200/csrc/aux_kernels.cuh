@@ -149,13 +149,13 @@ chain_export_nhwc(const __half* __restrict__ buf, __half* __restrict__ out, cons
     }
 }
 
-// Plain SpMM: one thread per (stored row, dense column).
+// Plain SpMM: one thread per (stored row, dense column); grid = (rows, column tiles).
 __global__ void simt_spmm(const int* __restrict__ blk_ptr, const int* __restrict__ blk_idx,
                           const __half* __restrict__ blk_val, const int* __restrict__ perm,
                           const __half* __restrict__ B, const __half* __restrict__ C, __half* __restrict__ D,
                           int M, int N, int V, float alpha, float beta) {
-    const int n = blockIdx.x * blockDim.x + threadIdx.x;
-    const int row = blockIdx.y;
+    const int n = blockIdx.y * blockDim.x + threadIdx.x;
+    const int row = blockIdx.x;
     if (n >= N || row >= M) return;
     const int blk = row / V, m = row % V;
     float acc = 0.f;
@@ -169,13 +169,14 @@ __global__ void simt_spmm(const int* __restrict__ blk_ptr, const int* __restrict
     D[(size_t)dst * N + n] = h;
 }
 
-// Plain SpConv straight from NHWC to NHWC: one thread per (output position, stored filter).
+// Plain SpConv straight from NHWC to NHWC: one thread per (output position, stored filter);
+// grid = (positions, filter tiles).
 __global__ void simt_spconv(const int* __restrict__ blk_ptr, const int* __restrict__ blk_idx,
                             const __half* __restrict__ blk_val, const int* __restrict__ perm,
                             const __half* __restrict__ in, __half* __restrict__ out, int Bn, int Hin, int Win,
                             int Cin, int F, int R, int S, int stride, int Ho, int Wo, int V, float alpha) {
-    const int f = blockIdx.x * blockDim.x + threadIdx.x;
-    const int q = blockIdx.y;  // output position (n, ho, wo)
+    const int f = blockIdx.y * blockDim.x + threadIdx.x;
+    const int q = blockIdx.x;  // output position (n, ho, wo)
     if (f >= F) return;
     const int wo = q % Wo, ho = (q / Wo) % Ho, n = q / (Wo * Ho);
     const int blk = f / V, m = f % V;

@@ -54,7 +54,7 @@
 
 namespace shflbw {
 
-constexpr long long kWaitLimitCycles = 400000000LL;   // ~0.2 s at 2 GHz
+constexpr long long kWaitLimitCycles = 400000000LL;   // default bound of every in-kernel wait: ~0.2 s at 2 GHz
 
 struct PanelParams {
     // sparse operand (kernel image)
@@ -63,6 +63,7 @@ struct PanelParams {
     const __half* blk_val;   // value panels of the padded rows, element order kval_index() (shflbw_internal.hpp)
     const int* perm;         // [M] or nullptr
     int* status_word;
+    long long wait_limit;    // SM clocks after which a barrier wait gives up (kWaitLimitCycles unless the host overrides it)
     float alpha, beta;
     int num_items, tiles_n;  // work items = row blocks x token tiles; item -> (item / tiles_n, item % tiles_n)
     unsigned long long* trace;  // tuning builds only: per-role timestamps of CTA 0
@@ -92,16 +93,28 @@ struct PanelParams {
 // 4 = chained SpConv with the operands swapped in the same way.
 constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2, kPanelSpmmRows = 3, kPanelConvChainRows = 4;
 
-template <int V, int TM, int KS_, int STAGES, int PW, int MODE>
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1>
 struct PanelCfg {
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
+    static constexpr int GROUPS = GROUPS_;                 // producer groups that take the stages in turn
+    static constexpr int LAG = LAG_;                       // a group publishes a stage while issuing its LAG-th next one
     // Warp w runs on scheduler partition w % 4.  The MMA warp (8) sits on partition 0 and no
     // producer shares it: warps 12, 16, 20... of the block stay idle.  The MMA warp executes a
     // few dozen instructions per stage and was measured at ~20 clk per instruction when
     // producer code kept evicting its lines from the partition's instruction cache.
-    static constexpr int WARPS = 9 + PW + (PW - 1) / 3;     // 8 epilogue + MMA + producers + idle
+    static constexpr int WARPS_USED = 9 + PW + (PW - 1) / 3;   // 8 epilogue + MMA + producers + idle
+    // Register budgets per role.  Up to 20 warps every thread can have the ~100 registers the
+    // epilogue wants.  Beyond that the block is padded to whole warpgroups (4 warps) and
+    // launched at 65536 / threads registers per thread; the producer / MMA warpgroups then give
+    // registers back (setmaxnreg.dec) and the two epilogue warpgroups take them (setmaxnreg.inc).
+    static constexpr bool REG_SPLIT = WARPS_USED > 20;
+    static constexpr int WARPS = REG_SPLIT ? (WARPS_USED + 3) / 4 * 4 : WARPS_USED;
     static constexpr int THREADS = WARPS * 32;
+    static constexpr int REGS_LEAN = 56;                                    // producers, MMA warp, idle warps
+    static constexpr int REGS_EPI_RAW = (65536 - (WARPS - 8) * 32 * REGS_LEAN) / 256 / 8 * 8;
+    static constexpr int REGS_EPI = REGS_EPI_RAW > 160 ? 160 : REGS_EPI_RAW;
+    static_assert(!REG_SPLIT || REGS_EPI >= 88, "epilogue register budget");
     static constexpr int G_ACC = KS * 256;                 // gathered tile of one accumulator: [KS][128] fp16
     static constexpr int G_BYTES = TM * G_ACC;
     static constexpr int W_BYTES = KS * V * 2;
@@ -112,7 +125,7 @@ struct PanelCfg {
     static constexpr int OUT_BYTES = 8 * 2048;
     static constexpr int BAR_BYTES = (STAGES * 2 + 8) * 8;   // mbarriers + tmem slot + abort flag
     static constexpr int TAB_BYTES = 512 * 8;               // per-CTA item table (kPanelMaxItemsPerCta entries)
-    static constexpr int IDX_RING = 8;                      // stages of row ids kept in shared memory
+    static constexpr int IDX_RING = GROUPS <= 2 ? 8 : 4 * GROUPS;   // stages of row ids kept in shared memory
     static constexpr int IDX_BYTES = IDX_RING * KS * 4;
     static constexpr int SMEM_BYTES = PIPE_BYTES + OUT_BYTES + BAR_BYTES + TAB_BYTES + IDX_BYTES + 1024;  // + align slack
     static constexpr bool SWAP = MODE == kPanelSpmmRows || MODE == kPanelConvChainRows;
@@ -123,7 +136,9 @@ struct PanelCfg {
     static_assert(V == 32 || V == 64 || V == 128, "row-block height");
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte swizzle-atom alignment");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
-    static_assert(KS % 16 == 0 && KS % PW == 0 && (KS / PW) % (32 / (T / 8)) == 0, "rows per producer warp");
+    static_assert(KS % 16 == 0 && PW % GROUPS == 0 && KS % (PW / GROUPS) == 0 && (KS / (PW / GROUPS)) % (32 / (T / 8)) == 0,
+                  "rows per producer warp");
+    static_assert(LAG >= 1 && LAG <= 2 && STAGES > GROUPS * LAG, "publish lag");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -143,10 +158,10 @@ __device__ __forceinline__ uint32_t tile32_off(int r, int c) { return (uint32_t)
 
 constexpr int kPanelMaxItemsPerCta = 512;  // capacity of the per-CTA item table
 
-template <int V, int TM, int KS_, int STAGES, int PW, int MODE>
-__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE>::THREADS, 1)
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1>
+__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_>::THREADS, 1)
 panel_umma_kernel(const PanelParams p) {
-    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE>;
+    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_>;
     constexpr bool SWAP = Cfg::SWAP;                                        // rows in TMEM lanes
     constexpr bool CONV = MODE == kPanelConv || MODE == kPanelConvChain || MODE == kPanelConvChainRows;  // implicit-GEMM gather
     constexpr bool CHAIN = MODE == kPanelConvChain || MODE == kPanelConvChainRows;
@@ -188,7 +203,7 @@ panel_umma_kernel(const PanelParams p) {
             // One arrival per producer WARP.  Per-thread deferred arrivals
             // (cp.async.mbarrier.arrive.noinc) were measured at ~3 clk of load/store-unit time
             // per thread, i.e. more than the copies themselves.
-            sm100::mbar_init(&full_bar[s], PW / 2);
+            sm100::mbar_init(&full_bar[s], PW / Cfg::GROUPS);
             sm100::mbar_init(&empty_bar[s], 1);   // one tcgen05.commit per drain
         }
         for (int b = 0; b < 2; ++b) {
@@ -216,8 +231,14 @@ panel_umma_kernel(const PanelParams p) {
     if (tid == 0) CTRACE(1);
 
     const int pidx = warp - 9 - (warp / 4 - 2);   // producer number of a producer warp (warps 9.. with warp % 4 != 0)
-    if (warp >= 9 && (warp & 3) == 0) {
-        // idle: keeps producers off the MMA warp's scheduler partition
+    if constexpr (Cfg::REG_SPLIT) {
+        // Whole warpgroups change their register budget together: warps 0-7 (epilogue) grow,
+        // every other warpgroup (MMA warp, producers, idle and padding warps) shrinks first.
+        if (warp < 8) sm100::setmaxnreg_inc<Cfg::REGS_EPI>();
+        else sm100::setmaxnreg_dec<Cfg::REGS_LEAN>();
+    }
+    if (warp >= 9 && ((warp & 3) == 0 || pidx >= PW)) {
+        // idle: keeps producers off the MMA warp's scheduler partition (or pads the last warpgroup)
     } else if (warp >= 9) {
         // ------------------------------------------------------------- producers ----
         // The PW producer warps form GROUPS groups that take the CTA's stages in turn (group g
@@ -225,14 +246,14 @@ panel_umma_kernel(const PanelParams p) {
         // (wait for the free stage, wait for its copies, publish) the other one issues copies,
         // so the load/store unit stays busy; with a single group the round trip (~400 clk)
         // simply added to every stage.
-        constexpr int GROUPS = 2;
+        constexpr int GROUPS = Cfg::GROUPS, LAG = Cfg::LAG;
         constexpr int GW = PW / GROUPS;        // warps that share one stage
         constexpr int RPW = KS / GW;           // rows of a stage owned by this warp
         constexpr int CPR = T / 8;             // 16-byte chunks per gathered row
         constexpr int RPI = 32 / CPR;          // rows per warp instruction (TM=2: 1, TM=1: 2)
         constexpr int NQ = RPW / RPI;          // gather copies per lane per stage
-        constexpr int XT = 8 / RPI;            // period of the swizzle term along q
-        static_assert(RPW % 8 == 0, "a producer warp owns whole 8-row swizzle groups");
+        constexpr int XT = NQ < 8 / RPI ? NQ : 8 / RPI;   // period of the swizzle term along q
+        static_assert(RPW % 8 == 0 || 8 % RPW == 0, "a producer warp owns whole 8-row swizzle groups or an aligned part of one");
         const int grp = pidx / GW, pw = pidx % GW;
         const int chunk = lane % CPR;          // this lane's chunk of the token tile
         const int sub = RPI == 2 ? (lane >> 4) : 0;
@@ -247,7 +268,7 @@ panel_umma_kernel(const PanelParams p) {
         uint32_t gx[XT];
 #pragma unroll
         for (int j = 0; j < XT; ++j) {
-            const int r7 = (j * RPI + sub) & 7;
+            const int r7 = (pw * RPW + j * RPI + sub) & 7;
             gx[j] = (uint32_t)(r7 * 128 + (((chunk & 7) ^ r7) << 4));
         }
         // A cursor walks the flattened (item, stage) sequence of this CTA using the item table.
@@ -276,6 +297,7 @@ panel_umma_kernel(const PanelParams p) {
             }
         };
         static_assert(2 * GROUPS + GROUPS <= Cfg::IDX_RING, "row-id ring too small");
+        static_assert(RPW <= 32, "one lane per row of the warp's share when prefetching ids");
 
         Cursor cur{0, 0, 0, 0, 0}, pre{0, 0, 0, 0, 0};
         enter(cur);
@@ -291,7 +313,9 @@ panel_umma_kernel(const PanelParams p) {
         __syncwarp();
 
         int it = 0;        // stage counter across items (all groups count the same sequence)
-        int prev_s = -1;   // this group's previous stage, published one iteration later
+        int pend[LAG];     // this group's stages not yet published, oldest first
+#pragma unroll
+        for (int i = 0; i < LAG; ++i) pend[i] = -1;
 #ifdef SHFLBW_COUNTERS
         long long pc_empty = 0, pc_n = 0, pc_t0 = clock64();
 #endif
@@ -327,7 +351,7 @@ panel_umma_kernel(const PanelParams p) {
 #endif
                     if (lane == 0)
                         sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
-                                                 SHFLBW_DEVSTAT_TIMEOUT_EMPTY, kWaitLimitCycles, 32);
+                                                 SHFLBW_DEVSTAT_TIMEOUT_EMPTY, p.wait_limit, 32);
                     __syncwarp();
 #ifdef SHFLBW_COUNTERS
                     pc_empty += clock64() - e0c; ++pc_n;
@@ -337,18 +361,19 @@ panel_umma_kernel(const PanelParams p) {
                 if (lane == 0) PTRACE(pidx, it, 0);
                 const int rows_valid = min(KS, ent.y - kt * KS);  // multiple of 16
                 const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
-                // The group's previous stage is published half-way through this stage's copies:
-                // the first half is committed as its own cp.async group, and "all but the newest
-                // group" then covers every copy of the previous stage -- issued at least half an
-                // issue phase ago, so the wait does not stall, while the tensor core gets the
-                // stage half an issue phase earlier than if it were published at the end.
+                // An earlier stage of the group (the LAG-th before this one) is published half-way
+                // through this stage's copies: every stage is committed as two cp.async groups, so
+                // "all but the newest 2*LAG - 1 groups" covers every copy of that stage -- issued
+                // at least LAG - 1/2 issue phases ago, so the wait does not stall, while the tensor
+                // core gets the stage half an issue phase earlier than if it were published at the
+                // end.
                 auto publish_prev = [&]() {
                     sm100::cp_async_commit();
-                    if (prev_s >= 0) {
-                        sm100::cp_async_wait<1>();
+                    if (pend[0] >= 0) {
+                        sm100::cp_async_wait<2 * LAG - 1>();
                         sm100::fence_proxy_async_smem();   // every lane: its generic-proxy writes -> tensor-core reads
                         __syncwarp();
-                        if (lane == 0) sm100::mbar_arrive(&full_bar[prev_s]);
+                        if (lane == 0) sm100::mbar_arrive(&full_bar[pend[0]]);
                     }
                 };
                 // Value panel slice [rows_valid][V]: stored in global memory in the byte order of
@@ -396,16 +421,20 @@ panel_umma_kernel(const PanelParams p) {
                 sm100::cp_async_commit();
                 if (pw == 0 && lane == 0) TRACE(0, it, 1);
                 if (lane == 0) PTRACE(pidx, it, 1);
-                prev_s = s;
+#pragma unroll
+                for (int i = 0; i + 1 < LAG; ++i) pend[i] = pend[i + 1];
+                pend[LAG - 1] = s;
                 if (pw == 0 && lane == 0) TRACE(0, it, 2);
                 if (lane == 0) PTRACE(pidx, it, 2);
             }
         }
-        // Publish the group's last stage.
+        // Publish the group's last stages.
         sm100::cp_async_wait<0>();
         sm100::fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && prev_s >= 0) sm100::mbar_arrive(&full_bar[prev_s]);
+#pragma unroll
+        for (int i = 0; i < LAG; ++i)
+            if (lane == 0 && pend[i] >= 0) sm100::mbar_arrive(&full_bar[pend[i]]);
         if (pw == 0 && lane == 0) CTRACE(2);
 #ifdef SHFLBW_COUNTERS
         if (lane == 0 && p.trace != nullptr && pidx < 8) {
@@ -433,6 +462,9 @@ panel_umma_kernel(const PanelParams p) {
 #ifdef SHFLBW_COUNTERS
             long long cnt_wait = 0, cnt_n = 0, cnt_acc = 0, cnt_t0 = clock64();
 #endif
+#ifdef SHFLBW_ABLATE
+            int held = -1;              // stage whose release waits for the next one (tuning: paired releases)
+#endif
             uint32_t s = 0, ph = 0;     // ring slot of stage `it` and the parity of its full barrier
             bool ready = false;         // that barrier was already seen complete
             for (int li = 0; li < nloc; ++li) {
@@ -444,7 +476,7 @@ panel_umma_kernel(const PanelParams p) {
 #endif
                 if (li >= 2)
                     sm100::mbar_wait_bounded(&acc_empty[b], ((li >> 1) - 1) & 1, cta_abort, p.status_word,
-                                             SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 20);
+                                             SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 20);
 #ifdef SHFLBW_COUNTERS
                 cnt_acc += clock64() - a0c;
 #endif
@@ -454,13 +486,13 @@ panel_umma_kernel(const PanelParams p) {
                     if (!ready) {
                         const long long w0 = clock64();
                         sm100::mbar_wait_bounded(&full_bar[s], ph, cta_abort, p.status_word,
-                                                 SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
+                                                 SHFLBW_DEVSTAT_TIMEOUT_FULL, p.wait_limit, 20);
                         cnt_wait += clock64() - w0; ++cnt_n;
                     }
 #else
                     if (!ready)
                         sm100::mbar_wait_bounded(&full_bar[s], ph, cta_abort, p.status_word,
-                                                 SHFLBW_DEVSTAT_TIMEOUT_FULL, kWaitLimitCycles, 20);
+                                                 SHFLBW_DEVSTAT_TIMEOUT_FULL, p.wait_limit, 20);
 #endif
                     TRACE(1, it, 0);
                     if (!(ablate & 16)) sm100::fence_proxy_async_smem();  // cp.async (generic proxy) data -> tensor-core (async proxy) reads
@@ -483,6 +515,15 @@ panel_umma_kernel(const PanelParams p) {
                         wdj += WSTEP >> 4;
                         accum = 1u;
                     }
+#ifdef SHFLBW_ABLATE
+                    if (ablate & 4096) {   // release stages in pairs: one pipeline drain per two stages
+                        if (held >= 0 || kt + 1 == num_k) {
+                            if (held >= 0) sm100::umma_commit(&empty_bar[held]);
+                            sm100::umma_commit(&empty_bar[s]);
+                            held = -1;
+                        } else held = (int)s;
+                    } else
+#endif
                     if (ablate & 64) sm100::mbar_arrive(&empty_bar[s]);
                     else sm100::umma_commit(&empty_bar[s]);  // stage may be refilled once these MMAs retire
                     TRACE(1, it, 1);
@@ -520,7 +561,7 @@ panel_umma_kernel(const PanelParams p) {
             const int b = li & 1;
             if (lane == 0)
                 sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
-                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, kWaitLimitCycles, 32);
+                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 32);
             __syncwarp();
             sm100::tc_fence_after_sync();
             if (tid == 0) TRACE(2, li, 0);

@@ -81,19 +81,46 @@ int host_pipeline(shflbw_matrix* m, cudaStream_t* s_in, cudaStream_t* s_k, cudaS
 using PanelKernel = void (*)(const shflbw::PanelParams);
 struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; };
 
-template <int V, int TM, int KS, int STAGES, int PW, int MODE>
+template <int V, int TM, int KS, int STAGES, int PW, int MODE, int GROUPS = 2, int LAG = 1>
 PanelChoice choice() {
-    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, MODE>;
-    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, MODE>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
+    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG>;
+    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
             Cfg::THREADS};
 }
 
+#ifdef SHFLBW_TUNE
+// Tuning builds only: SHFLBW_SHAPE="pw,groups,lag" picks the pipeline shape of the V = 64,
+// 256-token kernels (read at init and at exec, so a state follows the variable).
+template <int MODE>
+bool tuned_shape(PanelChoice* out) {
+    const char* e = getenv("SHFLBW_SHAPE");
+    if (!e) return false;
+    int pw = 0, groups = 0, lag = 0;
+    if (sscanf(e, "%d,%d,%d", &pw, &groups, &lag) != 3) return false;
+    switch (pw * 100 + groups * 10 + lag) {
+        case 821:  *out = choice<64, 2, 64, 5, 8, MODE, 2, 1>(); return true;
+        case 822:  *out = choice<64, 2, 64, 5, 8, MODE, 2, 2>(); return true;
+        case 811:  *out = choice<64, 2, 64, 5, 8, MODE, 1, 1>(); return true;
+        case 812:  *out = choice<64, 2, 64, 5, 8, MODE, 1, 2>(); return true;
+        case 1231: *out = choice<64, 2, 64, 5, 12, MODE, 3, 1>(); return true;
+        case 1621: *out = choice<64, 2, 64, 5, 16, MODE, 2, 1>(); return true;
+        case 1622: *out = choice<64, 2, 64, 5, 16, MODE, 2, 2>(); return true;
+        case 1611: *out = choice<64, 2, 64, 5, 16, MODE, 1, 1>(); return true;
+        case 1612: *out = choice<64, 2, 64, 5, 16, MODE, 1, 2>(); return true;
+        case 1641: *out = choice<64, 2, 64, 5, 16, MODE, 4, 1>(); return true;
+        default: return false;
+    }
+}
+#endif
+
 // Pipeline shape per (V, tile): non-zero columns per stage (KS) and ring depth (as many stages
-// as fit beside the 16 KB of epilogue tiles).  Eight producer warps: 12 and 16 were measured
-// and bring nothing.
+// as fit beside the 16 KB of epilogue tiles).
 template <int MODE>
 bool lookup(int V, int tile, PanelChoice* out) {
     if constexpr (MODE == shflbw::kPanelSpmmRows || MODE == shflbw::kPanelConvChainRows) {   // rows in TMEM lanes: V must be a legal UMMA M
+#ifdef SHFLBW_TUNE
+        if (V == 64 && tile == 256 && tuned_shape<MODE>(out)) return true;
+#endif
         switch (V * 1000 + tile) {
             case 64128:  *out = choice<64, 1, 64, 8, 8, MODE>(); return true;
             case 64256:  *out = choice<64, 2, 64, 5, 8, MODE>(); return true;
@@ -160,6 +187,31 @@ int pick_panel(int V, long long n_tokens, int row_blocks, long long padded_cols,
     if (!swapped && !lookup<MODE>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
     out->variant = swapped ? 1 : 0;
     CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
+    return SHFLBW_OK;
+}
+
+// Argument and range checks shared by every NHWC SpConv entry point.  The kernels index the
+// staged input with 32-bit element offsets and the output with 32-bit offsets whose all-ones
+// value is a sentinel, so both extents are bounded here, before anything is launched.
+struct ConvShape { int Ho, Wo, Bp; long long tokens, staged_elems; };
+int check_conv_call(const shflbw_matrix* f, int B, int Hin, int Win, int stride, const void* ifmap,
+                    const void* ofmap, ConvShape* cs) {
+    if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
+    if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
+    if (!on_current_device(*f)) return SHFLBW_ERR_NOT_ON_DEVICE;
+    if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
+    if (((uintptr_t)ifmap | (uintptr_t)ofmap) & 15) return SHFLBW_ERR_UNSUPPORTED;
+    if (B > (1 << 24) || Hin > (1 << 24) || Win > (1 << 24)) return SHFLBW_ERR_UNSUPPORTED;   // keeps the products below in 64 bits
+    cs->Ho = (Hin + stride - 1) / stride; cs->Wo = (Win + stride - 1) / stride;
+    cs->Bp = (B + 7) / 8 * 8;
+    cs->tokens = (long long)cs->Ho * cs->Wo * cs->Bp;
+    const long long plane = (long long)(Hin + f->R - 1) * (Win + f->S - 1);        // < 2^50
+    if (plane >= (1ll << 31) || cs->tokens >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+    cs->staged_elems = plane * cs->Bp;                                              // < 2^56
+    if (cs->staged_elems >= (1ll << 31) || cs->staged_elems * f->C >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
+    cs->staged_elems *= f->C;
+    if ((long long)B * cs->Ho * cs->Wo >= (1ll << 32) || (long long)B * cs->Ho * cs->Wo * f->F >= (1ll << 32) - 1)
+        return SHFLBW_ERR_UNSUPPORTED;                                              // 32-bit output offsets
     return SHFLBW_OK;
 }
 
@@ -263,7 +315,7 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
     // also instantiates, spmm/blockwise_library.cu:15-31) is served by the plain CUDA-core kernel.
     if (m->brow == 16 && kernel == SHFLBW_KERNEL_AUTO) kernel = SHFLBW_KERNEL_SIMT;
     if (kernel != SHFLBW_KERNEL_SIMT && m->brow != 32 && m->brow != 64 && m->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
-    if (kernel == SHFLBW_KERNEL_SIMT && m->nrow > 65535) return SHFLBW_ERR_UNSUPPORTED;   // one grid row per matrix row
+    if (kernel == SHFLBW_KERNEL_SIMT && (N + 127) / 128 > 65535) return SHFLBW_ERR_UNSUPPORTED;   // column tiles ride in grid.y
     if (N % 8) return SHFLBW_ERR_UNSUPPORTED;                   // 16-byte rows of fp16
     const uintptr_t al = (uintptr_t)B | (uintptr_t)D | (uintptr_t)C;
     if (al & 15) return SHFLBW_ERR_UNSUPPORTED;
@@ -278,7 +330,7 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
     out->perm = m->d_perm; out->status_word = m->d_status;
     if (kernel == SHFLBW_KERNEL_SIMT) {
         out->kernel = SHFLBW_KERNEL_SIMT;
-        out->block_x = 128; out->grid_x = (N + 127) / 128; out->grid_y = m->nrow;
+        out->block_x = 128; out->grid_x = m->nrow; out->grid_y = (N + 127) / 128;   // rows in grid.x: no 65535 limit
         out->tokens_per_cta = 128; out->stages = 0; out->shared_mem_size = 0;
     } else {
         PanelChoice ch;
@@ -315,13 +367,14 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         shflbw::PanelParams p{};
         p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
+        p.wait_limit = shflbw::kWaitLimitCycles;
         p.B = (const __half*)st->B; p.C = (const __half*)st->C; p.D = (__half*)st->D; p.N = st->N;
         p.num_items = st->num_items; p.tiles_n = st->tiles_n;
 #if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
         if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
         if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
 #endif
-        ch.fn<<<dim3(st->grid_x, st->grid_y), st->block_x, st->shared_mem_size, s>>>(p);
+        ch.fn<<<dim3(st->grid_x, st->grid_y), ch.threads, ch.smem, s>>>(p);
     }
     CK(cudaGetLastError());
     return SHFLBW_OK;
@@ -342,6 +395,8 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
     if (N % 8) return SHFLBW_ERR_UNSUPPORTED;
     int rc = shflbw_matrix_to_device(m);
     if (rc != SHFLBW_OK) return rc;
+    // Before any staging buffer or stream is made: they would belong to the wrong GPU.
+    if (!on_current_device(*m)) return SHFLBW_ERR_NOT_ON_DEVICE;
     const size_t bB = (size_t)m->ncol * N * 2, bD = (size_t)m->nrow * N * 2;
     if ((rc = ensure_buffer(&m->stage_in, &m->stage_in_bytes, bB)) != SHFLBW_OK) return rc;
     if ((rc = ensure_buffer(&m->stage_out, &m->stage_out_bytes, bD)) != SHFLBW_OK) return rc;
@@ -414,22 +469,14 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
                        void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
     if (!out) return SHFLBW_ERR_INVALID_ARG;
     std::memset(out, 0, sizeof *out);
-    if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
     if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
-    if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
-    if (!on_current_device(*f)) return SHFLBW_ERR_NOT_ON_DEVICE;
+    ConvShape cs;
+    int rc = check_conv_call(f, B, Hin, Win, stride, ifmap, ofmap, &cs);
+    if (rc != SHFLBW_OK) return rc;
     if (f->brow == 16 && kernel == SHFLBW_KERNEL_AUTO) kernel = SHFLBW_KERNEL_SIMT;   // as for SpMM
     if (kernel != SHFLBW_KERNEL_SIMT && f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
-    if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
-    if (((uintptr_t)ifmap | (uintptr_t)ofmap) & 15) return SHFLBW_ERR_UNSUPPORTED;
-    const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
-    const int Bp = (B + 7) / 8 * 8;
-    const long long tokens = (long long)Ho * Wo * Bp;
-    if (kernel == SHFLBW_KERNEL_SIMT && (long long)B * Ho * Wo > 65535) return SHFLBW_ERR_UNSUPPORTED;  // one grid row per position
-    // 32-bit element offsets into the staged (halo-padded) input.
-    const long long staged_elems = (long long)f->C * (Hin + f->R - 1) * (Win + f->S - 1) * Bp;
-    if (tokens >= (1ll << 31) || staged_elems >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
-    if ((long long)B * Ho * Wo * f->F >= (1ll << 32) - 1) return SHFLBW_ERR_UNSUPPORTED;  // 32-bit output offsets
+    const int Ho = cs.Ho, Wo = cs.Wo, Bp = cs.Bp;
+    const long long tokens = cs.tokens, staged_elems = cs.staged_elems;
 
     out->B = B; out->Hin = Hin; out->Win = Win; out->C = f->C; out->F = f->F; out->R = f->R; out->S = f->S;
     out->stride = stride; out->Ho = Ho; out->Wo = Wo; out->V = f->brow; out->Bp = Bp;
@@ -443,12 +490,13 @@ int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
     }
     if (kernel == SHFLBW_KERNEL_SIMT) {
         out->kernel = SHFLBW_KERNEL_SIMT;
-        out->block_x = 128; out->grid_x = (f->F + 127) / 128; out->grid_y = (unsigned)(B * Ho * Wo);
+        if ((f->F + 127) / 128 > 65535) return SHFLBW_ERR_UNSUPPORTED;
+        out->block_x = 128; out->grid_x = (unsigned)(B * Ho * Wo); out->grid_y = (f->F + 127) / 128;   // positions in grid.x
         out->init_success = 1;
         return SHFLBW_OK;
     }
     PanelChoice ch;
-    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
+    rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
     if (rc != SHFLBW_OK) return rc;
     out->kernel = SHFLBW_KERNEL_TCGEN05;
     out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
@@ -502,6 +550,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     shflbw::PanelParams p{};
     p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
     p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = 0.f;
+    p.wait_limit = shflbw::kWaitLimitCycles;
     p.N = st->Ho * st->Wo * st->Bp;
     p.Xs = (const __half*)(st->chain ? st->ifmap : st->staged_in);
     p.out = (__half*)(st->staged_out ? st->staged_out : st->ofmap);
@@ -547,6 +596,7 @@ int shflbw_spconv_host(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, 
         return SHFLBW_ERR_INVALID_ARG;
     int rc = shflbw_matrix_to_device(f);
     if (rc != SHFLBW_OK) return rc;
+    if (!on_current_device(*f)) return SHFLBW_ERR_NOT_ON_DEVICE;   // before staging buffers / streams are made
     const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
     const size_t img_in = (size_t)Hin * Win * f->C, img_out = (size_t)Ho * Wo * f->F;   // elements per image
     if ((rc = ensure_buffer(&f->stage_in, &f->stage_in_bytes, (size_t)B * img_in * 2)) != SHFLBW_OK) return rc;
@@ -679,14 +729,21 @@ int shflbw_spconv_chain_set_residual(shflbw_matrix_t* f, shflbw_spconv_state_t* 
     if (!f || !st || !st->init_success || !st->chain || !res_chain) return SHFLBW_ERR_INVALID_ARG;
     if (!on_current_device(*f) || st->blk_ptr != f->d_kptr) return SHFLBW_ERR_INVALID_ARG;
     if ((uintptr_t)res_chain & 15) return SHFLBW_ERR_UNSUPPORTED;
+    // A map buffer made by an earlier call for this state is one of the handle's retired buffers.
+    const int* prev_map = nullptr;
+    for (void* r : f->retired) if (r == (const void*)st->residual_map) prev_map = st->residual_map;
     st->residual = res_chain;
     st->residual_map = nullptr;
     if (map_host) {
         for (int i = 0; i < st->F; ++i)
             if (map_host[i] < 0 || map_host[i] >= st->F) return SHFLBW_ERR_BAD_FORMAT;
-        void* d = nullptr;
-        CK(cudaMalloc(&d, (size_t)st->F * sizeof(int)));
-        f->retired.push_back(d);                       // lives as long as the filter's device copy
+        // One device buffer per state: re-binding the residual of the same state (every step,
+        // say) overwrites it in place instead of allocating again.
+        void* d = const_cast<int*>(prev_map);
+        if (!d) {
+            CK(cudaMalloc(&d, (size_t)st->F * sizeof(int)));
+            f->retired.push_back(d);                   // lives as long as the filter's device copy
+        }
         CK(cudaMemcpy(d, map_host, (size_t)st->F * sizeof(int), cudaMemcpyHostToDevice));
         st->residual_map = (const int*)d;
     }
@@ -695,21 +752,20 @@ int shflbw_spconv_chain_set_residual(shflbw_matrix_t* f, shflbw_spconv_state_t* 
 
 int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, int Win, int stride,
                                       const void* ifmap, void* ofmap, float alpha, void* stream) {
-    if (!f || !ifmap || !ofmap || B <= 0 || Hin <= 0 || Win <= 0 || stride <= 0) return SHFLBW_ERR_INVALID_ARG;
-    if (!f->is_filter) return SHFLBW_ERR_INVALID_ARG;
-    if (!on_current_device(*f)) return SHFLBW_ERR_NOT_ON_DEVICE;
+    // Same argument and 32-bit range checks as shflbw_spconv_init: with an unpermuted filter the
+    // output goes straight to ofmap, so the scratch capacity alone would not bound its offsets.
+    ConvShape cs;
+    int rc = check_conv_call(f, B, Hin, Win, stride, ifmap, ofmap, &cs);
+    if (rc != SHFLBW_OK) return rc;
     if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
-    if (f->C % 8 || f->R > 255 || f->S > 255) return SHFLBW_ERR_UNSUPPORTED;
-    if (((uintptr_t)ifmap | (uintptr_t)ofmap) & 15) return SHFLBW_ERR_UNSUPPORTED;
-    const int Ho = (Hin + stride - 1) / stride, Wo = (Win + stride - 1) / stride;
-    const int Bp = (B + 7) / 8 * 8;
-    const long long tokens = (long long)Ho * Wo * Bp;
-    if ((long long)f->C * Hin * Win >= (1ll << 31) || tokens >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
     if (!f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
+    const int Ho = cs.Ho, Wo = cs.Wo, Bp = cs.Bp;
+    const long long tokens = cs.tokens;
 
-    // Capacity check first: nothing is launched when the shape does not fit.
+    // Capacity check first: nothing is launched when the shape does not fit.  (Both terms are
+    // below 2^33 after the checks above.)
     auto up256 = [](unsigned long long v) { return (v + 255ull) / 256ull * 256ull; };
-    const unsigned long long in_bytes = up256(2ull * f->C * (Hin + f->R - 1) * (Win + f->S - 1) * Bp);
+    const unsigned long long in_bytes = up256(2ull * (unsigned long long)cs.staged_elems);
     const unsigned long long out_bytes = f->row_permute ? up256(2ull * B * Ho * Wo * f->F) : 0ull;
     if (in_bytes + out_bytes > (unsigned long long)SHFLBW_STATIC_SCRATCH_BYTES) {
         snprintf(g_cuda_err, sizeof g_cuda_err,
@@ -734,7 +790,7 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     shflbw_spconv_state_t st;
     std::memset(&st, 0, sizeof st);
     PanelChoice ch;
-    int rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
+    rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
     if (rc != SHFLBW_OK) return rc;
     const int sms = sm_count();
     if (sms <= 0) return SHFLBW_ERR_CUDA;

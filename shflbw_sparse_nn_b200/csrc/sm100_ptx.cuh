@@ -115,6 +115,15 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ------------------------------------------------------- register budgets ----
+// Change the per-thread register budget of the executing warpgroup (4 consecutive warps, all
+// of which must execute the same instruction).  The count is a multiple of 8 in [24, 256].
+// .dec returns registers to the SM's pool at once; .inc waits until the pool holds enough.
+template <int N>
+__device__ __forceinline__ void setmaxnreg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N>
+__device__ __forceinline__ void setmaxnreg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ------------------------------------------------------------------- tcgen05 ----
 // TMEM allocation: one full warp; ncols a power of two in [32, 512].  The base address
 // (lane 0, first column) is written to *slot in shared memory.
