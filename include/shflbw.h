@@ -72,6 +72,14 @@ const char* shflbw_last_cuda_error(void);
 /* Library/ABI version, for binding sanity checks. */
 int shflbw_abi_version(void);
 
+/* Every wait inside the kernels (on a pipeline stage, an accumulator) is bounded: after this many
+ * SM clocks without progress the kernel records a SHFLBW_DEVSTAT_* code in the matrix's status
+ * word, stops issuing work, lets what is in flight land and returns; shflbw_matrix_device_status
+ * then reports SHFLBW_ERR_DEVICE_TIMEOUT and the context stays usable.  Default 400 000 000
+ * (~0.2 s); process-wide, applies to launches issued after the call.  No counterpart in the
+ * reference (its kernels have no waits that another agent completes). */
+int shflbw_set_wait_limit_cycles(long long cycles);
+
 /* ---------------------------------------------------------------- format builder ---- */
 
 /* Replaces BlockwiseSpMatrix<half>::init_random (block_sparse/spmm/blockwise_format.h:70-123)
@@ -166,6 +174,8 @@ typedef struct shflbw_spmm_state {
     const void* blk_val;     /* padded fp16 value panels, [rows][V] */
     const int* perm;         /* device row permutation or NULL */
     int* status_word;        /* device int: 0 ok, else a SHFLBW_DEVSTAT_* code */
+    int gather;              /* 0: cp.async gather, 1: TMA tile-gather through tmap_b */
+    unsigned long long tmap_b[16]; /* TMA tensor map of B (opaque 128 bytes, built at init from B and N) */
 } shflbw_spmm_state_t;
 
 /* Replaces SpmmBlockwiseOp::initialize / SpmmBlockwiseInitFn

@@ -37,6 +37,7 @@ class SpmmState(C.Structure):
         ("B", C.c_void_p), ("C", C.c_void_p), ("D", C.c_void_p),
         ("blk_ptr", C.c_void_p), ("blk_idx", C.c_void_p), ("blk_val", C.c_void_p),
         ("perm", C.c_void_p), ("status_word", C.c_void_p),
+        ("gather", C.c_int), ("tmap_b", C.c_ulonglong * 16),
     ]
 
 
@@ -65,6 +66,7 @@ _PROTOS = {
     "shflbw_strerror": (C.c_char_p, [C.c_int]),
     "shflbw_last_cuda_error": (C.c_char_p, []),
     "shflbw_abi_version": (C.c_int, []),
+    "shflbw_set_wait_limit_cycles": (C.c_int, [C.c_longlong]),
     "shflbw_matrix_create_random": (C.c_int, [C.c_int] * 4 + [C.c_float, C.c_int, C.c_uint, C.c_int, C.POINTER(_H)]),
     "shflbw_filter_create_random": (C.c_int, [C.c_int] * 6 + [C.c_float, C.c_int, C.c_uint, C.c_int, C.POINTER(_H)]),
     "shflbw_matrix_create_from_arrays": (C.c_int, [C.c_int] * 4 + [C.c_void_p] * 4 + [C.POINTER(_H)]),
@@ -123,21 +125,27 @@ def exported_symbols() -> list[str]:
     return sorted(_PROTOS)
 
 
+def load_library(path) -> C.CDLL:
+    """Load a build of the native library from `path` and set the prototypes of every declared
+    entry point on it (AttributeError if one is not exported)."""
+    path = Path(path)
+    if not path.exists():
+        raise RuntimeError(
+            f"{path} is missing: build it with `python -m shflbw_sparse_nn_b200.build` "
+            "(there is no CPU fallback for the CUDA path)")
+    handle = C.CDLL(str(path))
+    for name, (res, args) in _PROTOS.items():
+        fn = getattr(handle, name)
+        fn.restype = res
+        fn.argtypes = args
+    return handle
+
+
 def lib() -> C.CDLL:
     """Load (once) and return the native library; raises if it has not been built."""
     global _lib
     if _lib is None:
-        path = Path(LIB_PATH)
-        if not path.exists():
-            raise RuntimeError(
-                f"{path} is missing: build it with `python -m shflbw_sparse_nn_b200.build` "
-                "(there is no CPU fallback for the CUDA path)")
-        handle = C.CDLL(str(path))
-        for name, (res, args) in _PROTOS.items():
-            fn = getattr(handle, name)  # AttributeError if the symbol is not exported
-            fn.restype = res
-            fn.argtypes = args
-        _lib = handle
+        _lib = load_library(LIB_PATH)
     return _lib
 
 

@@ -61,6 +61,31 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+FAULT_LIB_PATH = PKG_DIR / "libshflbw_b200_faultinject.so"
+
+
+def build_fault_inject_library(force: bool = False) -> Path:
+    """The same library compiled with -DSHFLBW_FAULT_INJECT: it adds one entry point that makes a
+    producer warp withhold its barrier arrivals, so a test can watch a bounded in-kernel wait run
+    out (and the library recover) without faulting or hanging the GPU.  Test infrastructure: the
+    product library has no such switch."""
+    if not force and FAULT_LIB_PATH.exists():
+        built = FAULT_LIB_PATH.stat().st_mtime
+        if all(p.stat().st_mtime <= built for p in SOURCES + HEADERS):
+            return FAULT_LIB_PATH
+    cmd = [
+        _nvcc(), "-ccbin", "g++", "-O3", "-std=c++17",
+        "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+        "-Xcompiler", "-fPIC", "-shared", "-DSHFLBW_FAULT_INJECT",
+        "-I", str(REPO_ROOT / "include"),
+        "-o", str(FAULT_LIB_PATH),
+    ] + [str(s) for s in SOURCES]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed ({res.returncode}):\n{res.stdout}\n{res.stderr}")
+    return FAULT_LIB_PATH
+
+
 TOOLS_DIR = PKG_DIR / "bin"
 TOOL_SOURCE = PKG_DIR / "csrc" / "benchmark_cli.cu"
 

@@ -48,7 +48,7 @@ const char* kUsage =
 #endif
     "\t--d [density between 0~1]\n"
     "\t--sparsity-type [block]\n"
-    "\t--block-size [32/64/128]\n"
+    "\t--block-size [16/32/64/128]\n"
     "\tOptional cmdline args:\n"
     "\t--row-permute : run with a random row (filter) permutation\n"
     "\t--random : random seed (default 2021 for every run)\n"
@@ -132,7 +132,7 @@ int main(int argc, const char** argv) {
              "sparsity-pattern = %d\nrow-permute ? %d\n", a.m, a.n, a.k, a.density, a.seed, a.block, a.pattern, (int)a.permute);
     if (a.m <= 0 || a.n <= 0 || a.k <= 0 || a.density == 0.f) die("Forget to set m,n,k or density?", log);
 #endif
-    if (a.block != 32 && a.block != 64 && a.block != 128) die("Unsupported block size. Choose in 32/64/128.", log);
+    if (a.block != 16 && a.block != 32 && a.block != 64 && a.block != 128) die("Unsupported block size. Choose in 16/32/64/128.", log);
     if (a.pattern != 0) die("sparsity-pattern is not given or unsupported.", log);
     fputs(log, stderr);
 

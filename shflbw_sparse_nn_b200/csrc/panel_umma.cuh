@@ -56,17 +56,25 @@ namespace shflbw {
 
 constexpr long long kWaitLimitCycles = 400000000LL;   // default bound of every in-kernel wait: ~0.2 s at 2 GHz
 
-struct PanelParams {
+struct alignas(64) PanelParams {
+    // TMA gather only: tensor map of B ([K][N] fp16, box = 64 tokens x 1 row, 128-byte swizzle); first
+    // member so that it sits on the 64-byte boundary the copy engine wants
+    unsigned long long tmap_b[16];
     // sparse operand (kernel image)
     const int* blk_ptr;      // [X+1] padded offsets (multiples of 16)
     const int* blk_idx;      // padded column ids
     const __half* blk_val;   // value panels of the padded rows, element order kval_index() (shflbw_internal.hpp)
     const int* perm;         // [M] or nullptr
     int* status_word;
+    unsigned idx_limit;      // largest legal gather offset: K - 1 (SpMM, a row id) or the element offset of the last
+                             // (channel, tap) plane origin (SpConv); ids are clamped to it, so a corrupted id can
+                             // give wrong numbers but never an address outside the dense operand
     long long wait_limit;    // SM clocks after which a barrier wait gives up (kWaitLimitCycles unless the host overrides it)
     float alpha, beta;
     int num_items, tiles_n;  // work items = row blocks x token tiles; item -> (item / tiles_n, item % tiles_n)
     unsigned long long* trace;  // tuning builds only: per-role timestamps of CTA 0
+    int inject_from;         // fault-injection builds only (-DSHFLBW_FAULT_INJECT): from this stage number on, one
+                             // producer warp withholds its arrivals, so the consumer's bounded wait runs out (< 0: off)
     int ablate;              // tuning builds only (-DSHFLBW_ABLATE): 1 no MMA, 2 no gather, 4 no value copies, 8 no stores
     // SpMM
     const __half* B;         // [K][N]
@@ -80,6 +88,7 @@ struct PanelParams {
     int Bn, Bp, Hp, Wp, Cin, F, R, S, stride, Ho, Wo;
     // chained SpConv: out[f][OHp][OWp][Bp] with the next layer's halo (origin at (oph, opw))
     int OWp, oph, opw, out_plane, relu;
+    int out_logical;         // chained kernels: output plane of stored filter f is perm[f] (logical channel order) instead of f
     const __half* res;       // optional residual in the OUTPUT's geometry ([planes][OHp][OWp][Bp]) or nullptr
     const int* res_map;      // stored filter -> plane of `res` (nullptr: same index)
 };
@@ -93,8 +102,18 @@ struct PanelParams {
 // 4 = chained SpConv with the operands swapped in the same way.
 constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2, kPanelSpmmRows = 3, kPanelConvChainRows = 4;
 
-template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1>
+// GATHER: how the rows of the dense operand reach shared memory.
+//   kGatherCpAsync  16-byte cp.async per lane, written straight into the swizzled layout; the
+//                   producer warps wait for their copies and publish the stage themselves.
+//   kGatherTma      TMA tile::gather4: one instruction per lane fetches 4 rows x 64 tokens (the
+//                   tensor map covers this GPU's own B; no multicast), the copy engine applies
+//                   the 128-byte swizzle and completes the stage's barrier by byte count, so the
+//                   producers never wait for data.  SpMM with rows in lanes only.
+constexpr int kGatherCpAsync = 0, kGatherTma = 1;
+
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1, int GATHER_ = kGatherCpAsync>
 struct PanelCfg {
+    static constexpr bool TMA = GATHER_ == kGatherTma;
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
     static constexpr int GROUPS = GROUPS_;                 // producer groups that take the stages in turn
@@ -125,7 +144,9 @@ struct PanelCfg {
     static constexpr int OUT_BYTES = 8 * 2048;
     static constexpr int BAR_BYTES = (STAGES * 2 + 8) * 8;   // mbarriers + tmem slot + abort flag
     static constexpr int TAB_BYTES = 512 * 8;               // per-CTA item table (kPanelMaxItemsPerCta entries)
-    static constexpr int IDX_RING = GROUPS <= 2 ? 8 : 4 * GROUPS;   // stages of row ids kept in shared memory
+    static constexpr int IDX_AHEAD = LAG + 1;              // a group fetches row ids this many of its stages ahead
+    static constexpr int IDX_RING = (IDX_AHEAD + 1) * GROUPS <= 8 ? 8 : 16;   // stages of row ids kept in shared memory
+    static_assert((IDX_AHEAD + 1) * GROUPS <= IDX_RING, "row-id ring too small");
     static constexpr int IDX_BYTES = IDX_RING * KS * 4;
     static constexpr int SMEM_BYTES = PIPE_BYTES + OUT_BYTES + BAR_BYTES + TAB_BYTES + IDX_BYTES + 1024;  // + align slack
     static constexpr bool SWAP = MODE == kPanelSpmmRows || MODE == kPanelConvChainRows;
@@ -133,7 +154,9 @@ struct PanelCfg {
     static constexpr uint32_t ACC_COLS = SWAP ? T : TM * V; // fp32 columns of one accumulator set
     static_assert(!SWAP || V == 64 || V == 128, "rows-in-lanes needs a legal UMMA M");
     static constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // double buffered
-    static_assert(V == 32 || V == 64 || V == 128, "row-block height");
+    static_assert(V == 16 || V == 32 || V == 64 || V == 128, "row-block height");
+    static_assert(V != 16 || (TM == 1 && !SWAP), "16-row blocks: tokens in lanes, one 128-token accumulator");
+    static_assert(!TMA || MODE == kPanelSpmmRows, "TMA gather: SpMM with rows in lanes");
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte swizzle-atom alignment");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
     static_assert(KS % 16 == 0 && PW % GROUPS == 0 && KS % (PW / GROUPS) == 0 && (KS / (PW / GROUPS)) % (32 / (T / 8)) == 0,
@@ -158,10 +181,10 @@ __device__ __forceinline__ uint32_t tile32_off(int r, int c) { return (uint32_t)
 
 constexpr int kPanelMaxItemsPerCta = 512;  // capacity of the per-CTA item table
 
-template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1>
-__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_>::THREADS, 1)
-panel_umma_kernel(const PanelParams p) {
-    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_>;
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1, int GATHER_ = kGatherCpAsync>
+__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_, GATHER_>::THREADS, 1)
+panel_umma_kernel(const __grid_constant__ PanelParams p) {
+    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_, GATHER_>;
     constexpr bool SWAP = Cfg::SWAP;                                        // rows in TMEM lanes
     constexpr bool CONV = MODE == kPanelConv || MODE == kPanelConvChain || MODE == kPanelConvChainRows;  // implicit-GEMM gather
     constexpr bool CHAIN = MODE == kPanelConvChain || MODE == kPanelConvChainRows;
@@ -177,6 +200,7 @@ panel_umma_kernel(const PanelParams p) {
     uint64_t* acc_empty = acc_full + 2;                // [2] epilogue -> MMA
     uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
     volatile int* cta_abort = (volatile int*)(tmem_slot + 1);
+    uint64_t* drain_bar = acc_empty + 3;               // abort path only: MMA thread waits for its last MMAs
     int2* item_tab = (int2*)(bar_area + Cfg::BAR_BYTES);  // [nloc] (first padded row, padded row count)
     int* idx_ring = (int*)(bar_area + Cfg::BAR_BYTES + Cfg::TAB_BYTES);  // [IDX_RING][KS] row ids of upcoming stages
 
@@ -203,13 +227,16 @@ panel_umma_kernel(const PanelParams p) {
             // One arrival per producer WARP.  Per-thread deferred arrivals
             // (cp.async.mbarrier.arrive.noinc) were measured at ~3 clk of load/store-unit time
             // per thread, i.e. more than the copies themselves.
-            sm100::mbar_init(&full_bar[s], PW / Cfg::GROUPS);
+            // cp.async gather: one arrival per producer WARP of the group.  TMA gather: one arrival
+            // (with the stage's byte count) by the group's first warp.
+            sm100::mbar_init(&full_bar[s], Cfg::TMA ? 1 : PW / Cfg::GROUPS);
             sm100::mbar_init(&empty_bar[s], 1);   // one tcgen05.commit per drain
         }
         for (int b = 0; b < 2; ++b) {
             sm100::mbar_init(&acc_full[b], 1);
             sm100::mbar_init(&acc_empty[b], 8);   // one arrival per epilogue warp
         }
+        sm100::mbar_init(drain_bar, 1);
         *cta_abort = 0;
         sm100::mbar_init_fence();
     }
@@ -239,6 +266,85 @@ panel_umma_kernel(const PanelParams p) {
     }
     if (warp >= 9 && ((warp & 3) == 0 || pidx >= PW)) {
         // idle: keeps producers off the MMA warp's scheduler partition (or pads the last warpgroup)
+    } else if (warp >= 9 && Cfg::TMA) {
+        // ---------------------------------------------------- producers (TMA gather) ----
+        // A stage is KS gathered rows x T tokens = (KS/4) row quads x (T/64) column boxes, one
+        // tile::gather4 each (4 rows x 128 bytes, landing as half a swizzle atom).  The GW warps
+        // of a group split the stage's operations, one per lane; the group's first warp also
+        // posts the stage's byte count and the bulk copy of the value slice.  Nobody waits for
+        // data: the barrier completes when the bytes have arrived.
+        if constexpr (Cfg::TMA) {
+        constexpr int GROUPS = Cfg::GROUPS, GW = PW / GROUPS;
+        constexpr int BOXES = T / 64;                       // column boxes per row quad
+        constexpr int OPS = (KS / 4) * BOXES / GW;          // operations per warp per stage
+        static_assert((KS / 4) * BOXES % GW == 0 && OPS >= 1 && OPS <= 32, "gather4 operations per producer warp");
+        const int grp = pidx / GW, pw = pidx % GW;
+        const int opj = pw * OPS + lane;                    // this lane's operation of a stage
+        const int quad = opj / BOXES, cbox = opj % BOXES;
+        const bool issuer = lane < OPS;
+        const uint32_t dst_off = (uint32_t)((quad >> 1) * Cfg::KG_BYTES + cbox * 1024 + (quad & 1) * 512);
+        struct Cursor { int li, kt, num_k, row_begin, rows_total; };
+        auto enter = [&](Cursor& c) {
+            c.kt = 0;
+            while (c.li < nloc) {
+                const int2 e = item_tab[c.li];
+                c.row_begin = e.x; c.rows_total = e.y; c.num_k = (e.y + KS - 1) / KS;
+                if (c.num_k > 0) return;
+                ++c.li;
+            }
+            c.num_k = 0; c.row_begin = 0; c.rows_total = 0;
+        };
+        auto advance = [&](Cursor& c) { if (++c.kt >= c.num_k) { ++c.li; enter(c); } };
+        // The 4 row ids of this lane's quad, loaded one of the group's stages ahead (registers).
+        auto load_ids = [&](const Cursor& c) {
+            const int r = c.kt * KS + quad * 4;
+            if (issuer && c.li < nloc && r < c.rows_total) return __ldg((const int4*)(p.blk_idx + c.row_begin + r));
+            return make_int4(0, 0, 0, 0);
+        };
+        Cursor pre{0, 0, 0, 0, 0};
+        enter(pre);
+        for (int d = 0; d < grp; ++d) advance(pre);
+        int4 ids = load_ids(pre);
+        for (int g = 0; g < GROUPS; ++g) advance(pre);
+        int it = 0;
+        for (int li = 0; li < nloc; ++li) {
+            const int2 ent = item_tab[li];
+            const int num_k = (ent.y + KS - 1) / KS;
+            if (num_k == 0) continue;
+            const int item = (int)blockIdx.x + li * (int)gridDim.x;
+            const int col = (item % p.tiles_n) * T + cbox * 64;     // first token of this lane's box (beyond N: zero fill)
+            const __half* wsrc = p.blk_val + (size_t)ent.x * V;
+            for (int kt = 0; kt < num_k; ++kt, ++it) {
+                if ((it % GROUPS) != grp) continue;
+                const int s = it % STAGES;
+                if (it >= STAGES) {
+                    int ok = 1;
+                    if (lane == 0)
+                        ok = sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
+                                                      SHFLBW_DEVSTAT_TIMEOUT_EMPTY, p.wait_limit, 32);
+                    if (!__shfl_sync(0xffffffffu, ok, 0)) goto tma_producer_done;
+                }
+                const int rows_valid = min(KS, ent.y - kt * KS);    // multiple of 16
+                const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
+                if (pw == 0 && lane == 0) {
+                    const uint32_t wbytes = (uint32_t)(rows_valid * V * 2);
+#ifdef SHFLBW_FAULT_INJECT
+                    if (!(p.inject_from >= 0 && it >= p.inject_from && pidx == 0))   // the withheld arrival
+#endif
+                    sm100::mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(rows_valid * T * 2) + wbytes);
+                    if (!(ablate & 4)) sm100::bulk_copy_g2s(st_base + (uint32_t)Cfg::G_BYTES, wsrc + (size_t)kt * KS * V, wbytes, &full_bar[s]);
+                    else sm100::mbar_complete_tx(&full_bar[s], wbytes);
+                }
+                if (issuer && quad * 4 < rows_valid) {
+                    if (!(ablate & 2)) sm100::tma_gather4(st_base + dst_off, p.tmap_b, col, ids.x, ids.y, ids.z, ids.w, &full_bar[s]);
+                    else sm100::mbar_complete_tx(&full_bar[s], 512u);
+                }
+                ids = load_ids(pre);
+                for (int g = 0; g < GROUPS; ++g) advance(pre);
+            }
+        }
+    tma_producer_done:;
+        }
     } else if (warp >= 9) {
         // ------------------------------------------------------------- producers ----
         // The PW producer warps form GROUPS groups that take the CTA's stages in turn (group g
@@ -285,8 +391,10 @@ panel_umma_kernel(const PanelParams p) {
         };
         auto advance = [&](Cursor& c) { if (++c.kt >= c.num_k) { ++c.li; enter(c); } };
         // Row ids are prefetched with 4-byte cp.async into a shared-memory ring (slot = stage %
-        // IDX_RING; this warp owns entries [pw*RPW, pw*RPW + RPW) of its group's slots), two of
-        // the group's stages ahead, so they land with the copies awaited one iteration earlier.
+        // IDX_RING; this warp owns entries [pw*RPW, pw*RPW + RPW) of its group's slots), LAG + 1 of
+        // the group's stages ahead: they travel in the first cp.async group of a stage, and the
+        // publish step of the group's (LAG + 1)-th stage before the one that reads them is the
+        // last wait that is certain to cover that group.
         // (A register prefetch would stall: rotating the registers waits for the load in flight.)
         auto prefetch_idx = [&](const Cursor& c, int stage_no) {
             if (lane < RPW && !(ablate & 2048)) {
@@ -296,7 +404,6 @@ panel_umma_kernel(const PanelParams p) {
                                   ok ? p.blk_idx + c.row_begin + r : p.blk_idx, ok ? 4u : 0u);
             }
         };
-        static_assert(2 * GROUPS + GROUPS <= Cfg::IDX_RING, "row-id ring too small");
         static_assert(RPW <= 32, "one lane per row of the warp's share when prefetching ids");
 
         Cursor cur{0, 0, 0, 0, 0}, pre{0, 0, 0, 0, 0};
@@ -304,7 +411,7 @@ panel_umma_kernel(const PanelParams p) {
         pre = cur;
         for (int d = 0; d < grp; ++d) advance(pre);            // the group's first stage
 #pragma unroll 1
-        for (int d = 0; d < 2; ++d) {                          // ids of its first two stages
+        for (int d = 0; d < Cfg::IDX_AHEAD; ++d) {             // ids of its first stages
             prefetch_idx(pre, grp + d * GROUPS);
             for (int g = 0; g < GROUPS; ++g) advance(pre);
         }
@@ -345,14 +452,15 @@ panel_umma_kernel(const PanelParams p) {
             for (int kt = 0; kt < num_k; ++kt, ++it) {
                 if ((it % GROUPS) != grp) continue;            // the other group's stage
                 const int s = it % STAGES, s_idx = it % Cfg::IDX_RING;
-                if (it >= STAGES) {  // one lane polls; the warp follows through __syncwarp
+                if (it >= STAGES) {  // one lane polls; the warp follows through the broadcast of its result
 #ifdef SHFLBW_COUNTERS
                     const long long e0c = clock64();
 #endif
+                    int ok = 1;
                     if (lane == 0)
-                        sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
-                                                 SHFLBW_DEVSTAT_TIMEOUT_EMPTY, p.wait_limit, 32);
-                    __syncwarp();
+                        ok = sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
+                                                      SHFLBW_DEVSTAT_TIMEOUT_EMPTY, p.wait_limit, 32);
+                    if (!__shfl_sync(0xffffffffu, ok, 0)) goto producer_done;   // timed out or aborted: stop issuing
 #ifdef SHFLBW_COUNTERS
                     pc_empty += clock64() - e0c; ++pc_n;
 #endif
@@ -373,6 +481,9 @@ panel_umma_kernel(const PanelParams p) {
                         sm100::cp_async_wait<2 * LAG - 1>();
                         sm100::fence_proxy_async_smem();   // every lane: its generic-proxy writes -> tensor-core reads
                         __syncwarp();
+#ifdef SHFLBW_FAULT_INJECT
+                        if (p.inject_from >= 0 && it >= p.inject_from && pidx == 0) return;   // the withheld arrival
+#endif
                         if (lane == 0) sm100::mbar_arrive(&full_bar[pend[0]]);
                     }
                 };
@@ -384,7 +495,7 @@ panel_umma_kernel(const PanelParams p) {
                     sm100::mbar_expect_tx(&full_bar[s], wbytes);
                     sm100::bulk_copy_g2s(st_base + (uint32_t)Cfg::G_BYTES, wsrc + (size_t)kt * KS * V, wbytes, &full_bar[s]);
                 }
-                prefetch_idx(pre, it + 2 * GROUPS);            // joins this iteration's cp.async group
+                prefetch_idx(pre, it + Cfg::IDX_AHEAD * GROUPS);   // joins this iteration's first cp.async group
                 for (int g = 0; g < GROUPS; ++g) advance(pre);
                 const int* ids = idx_ring + s_idx * KS;  // landed: their group was awaited last iteration
 
@@ -394,7 +505,7 @@ panel_umma_kernel(const PanelParams p) {
                 if constexpr (!CONV) {
                     int idr[NQ];
 #pragma unroll
-                    for (int q = 0; q < NQ; ++q) idr[q] = ids[rbase + q * RPI];
+                    for (int q = 0; q < NQ; ++q) idr[q] = (int)min((unsigned)ids[rbase + q * RPI], p.idx_limit);
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) {
                         if (q == NQ / 2) publish_prev();
@@ -406,7 +517,8 @@ panel_umma_kernel(const PanelParams p) {
                     // Column ids arrive decoded (c | r << 16 | s << 24).  Lane j < RPW turns row
                     // pw*RPW + j into an element offset once; the copies fetch it by shuffle.
                     const int idv = ids[pw * RPW + (lane % RPW)];
-                    const int delta = ((idv & 0xffff) * (p.Hp * p.Wp) + ((idv >> 16) & 0xff) * p.Wp + ((idv >> 24) & 0xff)) * p.Bp;
+                    const int delta = (int)min((unsigned)(((idv & 0xffff) * (p.Hp * p.Wp) + ((idv >> 16) & 0xff) * p.Wp + ((idv >> 24) & 0xff)) * p.Bp),
+                                               p.idx_limit);
                     int dq[NQ];
 #pragma unroll
                     for (int q = 0; q < NQ; ++q) dq[q] = __shfl_sync(0xffffffffu, delta, q * RPI + sub);
@@ -428,7 +540,8 @@ panel_umma_kernel(const PanelParams p) {
                 if (lane == 0) PTRACE(pidx, it, 2);
             }
         }
-        // Publish the group's last stages.
+    producer_done:
+        // Publish the group's last stages (after a failed wait: just wait for the copies in flight).
         sm100::cp_async_wait<0>();
         sm100::fence_proxy_async_smem();
         __syncwarp();
@@ -450,10 +563,11 @@ panel_umma_kernel(const PanelParams p) {
         // tcgen05.mma instructions directly limits the tensor-pipe issue rate.
         const uint64_t gdesc0 = sm100::make_smem_desc(smem_base, 1024, Cfg::KG_BYTES, sm100::kSwizzle128B);
         const uint64_t wdesc0 =
-            V == 32 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 512, 512, sm100::kSwizzle64B)
+            V == 16 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 256, 256, sm100::kSwizzle32B)
+          : V == 32 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 512, 512, sm100::kSwizzle64B)
           : V == 64 ? sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 1024, sm100::kSwizzle128B)
                     : sm100::make_smem_desc(smem_base + Cfg::G_BYTES, 1024, 2048, sm100::kSwizzle128B);
-        constexpr uint32_t WSTEP = V == 32 ? 1024 : V == 64 ? 2048 : 4096;  // bytes per K-step of the value tile
+        constexpr uint32_t WSTEP = V * 32;  // bytes per K-step (16 rows) of the value tile
         // One thread runs the whole role (tcgen05.mma / commit are single-thread instructions):
         // no per-stage warp synchronisation, and the ring slot and its parity are carried
         // instead of being recomputed by division.
@@ -474,9 +588,9 @@ panel_umma_kernel(const PanelParams p) {
 #ifdef SHFLBW_COUNTERS
                 const long long a0c = clock64();
 #endif
-                if (li >= 2)
-                    sm100::mbar_wait_bounded(&acc_empty[b], ((li >> 1) - 1) & 1, cta_abort, p.status_word,
-                                             SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 20);
+                if (li >= 2 && !sm100::mbar_wait_bounded(&acc_empty[b], ((li >> 1) - 1) & 1, cta_abort, p.status_word,
+                                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 20))
+                    break;                                   // timed out or aborted: issue nothing more
 #ifdef SHFLBW_COUNTERS
                 cnt_acc += clock64() - a0c;
 #endif
@@ -490,9 +604,9 @@ panel_umma_kernel(const PanelParams p) {
                         cnt_wait += clock64() - w0; ++cnt_n;
                     }
 #else
-                    if (!ready)
-                        sm100::mbar_wait_bounded(&full_bar[s], ph, cta_abort, p.status_word,
-                                                 SHFLBW_DEVSTAT_TIMEOUT_FULL, p.wait_limit, 20);
+                    if (!ready && !sm100::mbar_wait_bounded(&full_bar[s], ph, cta_abort, p.status_word,
+                                                            SHFLBW_DEVSTAT_TIMEOUT_FULL, p.wait_limit, 20))
+                        goto mma_done;                       // timed out or aborted: issue nothing more
 #endif
                     TRACE(1, it, 0);
                     if (!(ablate & 16)) sm100::fence_proxy_async_smem();  // cp.async (generic proxy) data -> tensor-core (async proxy) reads
@@ -540,6 +654,13 @@ panel_umma_kernel(const PanelParams p) {
                 o[0] = cnt_wait; o[1] = cnt_n; o[2] = cnt_acc; o[3] = clock64() - cnt_t0; o[4] = it;
             }
 #endif
+        mma_done:
+            if (*cta_abort) {
+                // Aborted: the MMAs issued so far must retire before TMEM is freed and the block's
+                // shared memory goes away.  One more commit, awaited with its own (short) limit.
+                sm100::umma_commit(drain_bar);
+                sm100::mbar_wait_bounded(drain_bar, 0, cta_abort, p.status_word, 0, 4000000LL, 100, /*heed_abort=*/false);
+            }
         }
         __syncwarp();
         if (lane == 0) CTRACE(3);
@@ -548,8 +669,9 @@ panel_umma_kernel(const PanelParams p) {
         // Eight warps: warp w reads TMEM lane quadrant w % 4 (tokens) and half w / 4 of the
         // accumulator columns (the block's output rows / filters).
         const int quad = warp & 3, half_id = warp >> 2;
-        constexpr int HALVES = Cfg::ACC_COLS >= 64 ? 2 : 1;   // a 32-column accumulator is not split
+        constexpr int HALVES = Cfg::ACC_COLS >= 64 ? 2 : 1;   // a 16- or 32-column accumulator is not split
         constexpr int COLS = Cfg::ACC_COLS / HALVES;          // fp32 columns handled by this warp
+        constexpr int CW = COLS < 32 ? COLS : 32;             // columns per pass through the 2 KB tile
         const bool reads = half_id < HALVES;
         const __half alpha1 = __float2half_rn(p.alpha), beta1 = __float2half_rn(p.beta);
         const __half2 alpha2 = __half2half2(alpha1);
@@ -559,10 +681,11 @@ panel_umma_kernel(const PanelParams p) {
             const int n0 = (item % p.tiles_n) * T;
             const bool has_k = item_tab[li].y > 0 && !(ablate & 1);
             const int b = li & 1;
+            int acc_ok = 1;
             if (lane == 0)
-                sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
-                                         SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 32);
-            __syncwarp();
+                acc_ok = sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
+                                                  SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 32);
+            if (!__shfl_sync(0xffffffffu, acc_ok, 0)) break;    // timed out or aborted: store nothing more
             sm100::tc_fence_after_sync();
             if (tid == 0) TRACE(2, li, 0);
             if constexpr (SWAP) {
@@ -579,7 +702,10 @@ panel_umma_kernel(const PanelParams p) {
                 const int m = quad * LR + (lane < LR ? lane : 0);
                 uint32_t my_roff;                                        // element offset of this lane's output row
                 if constexpr (CHAIN) {
-                    my_roff = (uint32_t)(blk * V + m) * (uint32_t)p.out_plane;   // stored filter order
+                    // plane of this filter: stored order between chained layers, logical order when the
+                    // planes are about to be transposed to NHWC
+                    const int plane = (p.out_logical && p.perm) ? __ldg(p.perm + blk * V + m) : blk * V + m;
+                    my_roff = (uint32_t)plane * (uint32_t)p.out_plane;
                 } else {
                     const int drow = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
                     my_roff = (uint32_t)drow * (uint32_t)p.N;
@@ -720,30 +846,32 @@ panel_umma_kernel(const PanelParams p) {
             }
             const __half2 zero2 = __float2half2_rn(0.f);
 #pragma unroll 1
-            for (int cc = 0; cc < COLS; cc += 32) {
+            for (int cc = 0; cc < COLS; cc += CW) {
                 uint32_t roff[4];                                        // D offsets of rows cc + 8i + lane/4
                 uint32_t rres[4] = {0u, 0u, 0u, 0u};                     // chained: residual offsets of those rows
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
+                for (int i = 0; i < CW / 8; ++i) {
                     const int m = mbase + cc + 8 * i + (lane >> 2);
                     if constexpr (MODE == kPanelSpmm) {
                         const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
                         roff[i] = (uint32_t)row * (uint32_t)p.N;
                     } else {
-                        roff[i] = (uint32_t)(blk * V + m) * (uint32_t)p.out_plane;   // stored filter order
+                        const int plane = (p.out_logical && p.perm) ? __ldg(p.perm + blk * V + m) : blk * V + m;
+                        roff[i] = (uint32_t)plane * (uint32_t)p.out_plane;           // stored (chained) or logical order
                         if (p.res) rres[i] = (uint32_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (uint32_t)p.out_plane;
                     }
                 }
                 {
-                    uint32_t r[32];                       // the chunk's 32 accumulator columns of this token
+                    uint32_t r[CW];                       // the chunk's accumulator columns of this token
                     if (has_k && reads) {
-                        sm100::tmem_ld_32x32b_x32(acc_base + cc, r);
+                        if constexpr (CW == 32) sm100::tmem_ld_32x32b_x32(acc_base + cc, r);
+                        else sm100::tmem_ld_32x32b_x16(acc_base + cc, r);
                         sm100::tmem_ld_wait();
                     } else {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) r[e] = 0u;
+                        for (int e = 0; e < CW; ++e) r[e] = 0u;
                     }
-                    if (cc + 32 >= COLS) {  // last TMEM read of this item by this warp: release the buffer
+                    if (cc + CW >= COLS) {  // last TMEM read of this item by this warp: release the buffer
                         sm100::tc_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
@@ -752,7 +880,7 @@ panel_umma_kernel(const PanelParams p) {
                     // Same epilogue arithmetic as the reference: round to fp16, then alpha (and
                     // beta * C, applied after the transpose) in fp16.
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
+                    for (int e = 0; e < CW; ++e) {
                         __half h = __float2half_rn(__uint_as_float(r[e]));
                         if (!use_c) h = __hmul(h, alpha1);
                         my_tile[e * 32 + lane] = h;
@@ -761,7 +889,7 @@ panel_umma_kernel(const PanelParams p) {
                 __syncwarp();
                 if (!(ablate & 512)) {
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
+                    for (int i = 0; i < CW / 8; ++i) {
                         uint4 v = *(const uint4*)(my_tile + (8 * i + (lane >> 2)) * 32 + tg * 8);
                         if (ok_g) {
                             const size_t off = (size_t)roff[i] + (size_t)goff;
@@ -799,9 +927,9 @@ panel_umma_kernel(const PanelParams p) {
             // position's 64 contiguous bytes.
             uint8_t* my_tile = smem + Cfg::PIPE_BYTES + warp * 2048;
 #pragma unroll 1
-            for (int cc = 0; cc < COLS; cc += 32) {
+            for (int cc = 0; cc < COLS; cc += CW) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                for (int j = 0; j < CW / 8; ++j) {
                     const int c0 = cc + j * 8;
                     uint32_t r[8];
                     if (has_k && reads) {
@@ -830,7 +958,7 @@ panel_umma_kernel(const PanelParams p) {
                     for (int i = 0; i < 4; ++i) {
                         const int row = i * 8 + (lane >> 2), c = lane & 3;
                         const uint4 v = *(const uint4*)(my_tile + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
-                        if (row_off[i] != 0xffffffffu) *(uint4*)(p.out + (size_t)row_off[i] + cc + c * 8) = v;
+                        if (row_off[i] != 0xffffffffu && c < CW / 8) *(uint4*)(p.out + (size_t)row_off[i] + cc + c * 8) = v;
                     }
                 }
                 __syncwarp();
@@ -841,6 +969,14 @@ panel_umma_kernel(const PanelParams p) {
         if (tid == 0) CTRACE(4);
     }
 
+    if (*cta_abort) {
+        // A wait gave up somewhere in this block.  Every role has stopped issuing work; what is
+        // still in flight -- bulk copies of value slices (a few KB each) and gathers whose
+        // groups were awaited above -- gets a bounded ~100 us to land before the shared memory
+        // is released.
+        const long long t0 = clock64();
+        while (clock64() - t0 < 200000LL) __nanosleep(1000);
+    }
     sm100::tc_fence_before_sync();
     __syncthreads();
     if (tid == 0) TRACE(3, 0, 1);

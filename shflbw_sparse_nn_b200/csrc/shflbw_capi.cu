@@ -9,6 +9,8 @@
 //   block_sparse/spmm/blockwise_op.h:73-132, 169-209   initialize / operator() / InitFn / ExecFn
 //   block_sparse/spconv/blockwise_op.h:70-131, 148-187
 
+#include <cuda.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -20,6 +22,11 @@
 namespace {
 
 thread_local char g_cuda_err[256] = "";
+
+// Bound of the kernels' barrier waits in SM clocks, and (fault-injection builds) the stage from
+// which one producer warp withholds its arrivals.  Process-wide; read when a launch is issued.
+long long g_wait_limit = shflbw::kWaitLimitCycles;
+int g_inject_from = -1;
 
 bool cuda_ok(cudaError_t e, const char* what) {
     if (e == cudaSuccess) return true;
@@ -79,13 +86,43 @@ int host_pipeline(shflbw_matrix* m, cudaStream_t* s_in, cudaStream_t* s_k, cudaS
 
 // ---- kernel table -------------------------------------------------------------------
 using PanelKernel = void (*)(const shflbw::PanelParams);
-struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; };
+struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; int gather; };
 
-template <int V, int TM, int KS, int STAGES, int PW, int MODE, int GROUPS = 2, int LAG = 1>
+template <int V, int TM, int KS, int STAGES, int PW, int MODE, int GROUPS = 2, int LAG = 1, int GATHER = shflbw::kGatherCpAsync>
 PanelChoice choice() {
-    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG>;
-    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG>, (size_t)Cfg::SMEM_BYTES, Cfg::T, STAGES, PW,
-            Cfg::THREADS};
+    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG, GATHER>;
+    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG, GATHER>, (size_t)Cfg::SMEM_BYTES, Cfg::T,
+            STAGES, PW, Cfg::THREADS, 0, GATHER};
+}
+
+// TMA tensor map of the dense operand B ([K][N] fp16 row-major): box = 64 tokens x 1 row (what one
+// row of a tile::gather4 fetches), 128-byte swizzle (the layout tcgen05.mma reads), zero fill
+// outside the tensor.  The driver entry point is looked up once.
+int encode_b_map(const void* B, int K, int N, unsigned long long out[16]) {
+    typedef CUresult (*Encode)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static Encode enc = nullptr;
+    if (!enc) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
+        if (!fn || qr != cudaDriverEntryPointSuccess) return SHFLBW_ERR_CUDA;
+        enc = (Encode)fn;
+    }
+    static_assert(sizeof(CUtensorMap) == 128, "tensor map size");
+    alignas(64) CUtensorMap tm;
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)K}, strides[1] = {(cuuint64_t)N * 2};
+    const cuuint32_t box[2] = {64, 1}, estr[2] = {1, 1};
+    const CUresult r = enc(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(B), dims, strides, box, estr,
+                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_cuda_err, sizeof g_cuda_err, "cuTensorMapEncodeTiled failed: %d", (int)r);
+        return SHFLBW_ERR_CUDA;
+    }
+    std::memcpy(out, &tm, 128);
+    return SHFLBW_OK;
 }
 
 #ifdef SHFLBW_TUNE
@@ -108,8 +145,20 @@ bool tuned_shape(PanelChoice* out) {
         case 1611: *out = choice<64, 2, 64, 5, 16, MODE, 1, 1>(); return true;
         case 1612: *out = choice<64, 2, 64, 5, 16, MODE, 1, 2>(); return true;
         case 1641: *out = choice<64, 2, 64, 5, 16, MODE, 4, 1>(); return true;
-        default: return false;
+        default: break;
     }
+    if constexpr (MODE == shflbw::kPanelSpmmRows) {   // lag 0: TMA gather
+        switch (pw * 100 + groups * 10 + lag) {
+            case 410:  *out = choice<64, 2, 64, 5, 4, MODE, 1, 1, shflbw::kGatherTma>(); return true;
+            case 810:  *out = choice<64, 2, 64, 5, 8, MODE, 1, 1, shflbw::kGatherTma>(); return true;
+            case 820:  *out = choice<64, 2, 64, 5, 8, MODE, 2, 1, shflbw::kGatherTma>(); return true;
+            case 1610: *out = choice<64, 2, 64, 5, 16, MODE, 1, 1, shflbw::kGatherTma>(); return true;
+            case 1620: *out = choice<64, 2, 64, 5, 16, MODE, 2, 1, shflbw::kGatherTma>(); return true;
+            case 1640: *out = choice<64, 2, 64, 5, 16, MODE, 4, 1, shflbw::kGatherTma>(); return true;
+            default: break;
+        }
+    }
+    return false;
 }
 #endif
 
@@ -129,6 +178,10 @@ bool lookup(int V, int tile, PanelChoice* out) {
             default: return false;
         }
     } else {
+        if constexpr (MODE == shflbw::kPanelSpmm || MODE == shflbw::kPanelConv) {
+            // 16-row blocks: UMMA N = 16, one 128-token accumulator per item (18 KB stages)
+            if (V == 16 && tile == 128) { *out = choice<16, 1, 64, 8, 8, MODE>(); return true; }
+        }
         switch (V * 1000 + tile) {
             case 32128:  *out = choice<32, 1, 64, 8, 8, MODE>(); return true;    // 20 KB stages
             case 32256:  *out = choice<32, 2, 64, 5, 8, MODE>(); return true;    // 36 KB
@@ -170,6 +223,7 @@ int pick_panel(int V, long long n_tokens, int row_blocks, long long padded_cols,
     const long long waves256 = (items256 + sms - 1) / sms, waves128 = (items128 + sms - 1) / sms;
     if (n_tokens <= 128 || waves128 * 2 < waves256 * 3) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
+    if (V == 16) tile = 128;   // the only shape built for 16-row blocks
     // SpMM and chained SpConv with V = 64 / 128 can run with the operands swapped (rows in TMEM
     // lanes, one MMA per 16 columns for the whole token tile); SHFLBW_SWAP=0|1 forces the choice
     // (tuning aid).
@@ -251,6 +305,18 @@ extern "C" {
 
 const char* shflbw_last_cuda_error(void) { return g_cuda_err; }
 
+int shflbw_set_wait_limit_cycles(long long cycles) {
+    if (cycles < 1000) return SHFLBW_ERR_INVALID_ARG;
+    g_wait_limit = cycles;
+    return SHFLBW_OK;
+}
+
+#ifdef SHFLBW_FAULT_INJECT
+// Test builds only: launches issued after this call run with one producer warp withholding its
+// barrier arrivals from stage `stage` on (< 0: off), so that the consumer's bounded wait gives up.
+int shflbw_debug_withhold_arrivals_from(int stage) { g_inject_from = stage; return SHFLBW_OK; }
+#endif
+
 int shflbw_matrix_to_device(shflbw_matrix_t* m) {
     if (!m) return SHFLBW_ERR_INVALID_ARG;
     if (m->d_meta) return SHFLBW_OK;
@@ -311,10 +377,10 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
     if (beta != 0.f && !C) return SHFLBW_ERR_INVALID_ARG;
     if (!on_current_device(*m)) return SHFLBW_ERR_NOT_ON_DEVICE;  // reference: assert(device_synced)
     if (m->bcol != 1) return SHFLBW_ERR_UNSUPPORTED;            // reference: assert(bcol == BK)
-    // Row-block heights 32/64/128 run on the tensor-core kernel.  V = 16 (which the reference
-    // also instantiates, spmm/blockwise_library.cu:15-31) is served by the plain CUDA-core kernel.
-    if (m->brow == 16 && kernel == SHFLBW_KERNEL_AUTO) kernel = SHFLBW_KERNEL_SIMT;
-    if (kernel != SHFLBW_KERNEL_SIMT && m->brow != 32 && m->brow != 64 && m->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    // Row-block heights 16/32/64/128 (what the reference instantiates, spmm/blockwise_library.cu:15-31)
+    // run on the tensor-core kernel.
+    if (kernel != SHFLBW_KERNEL_SIMT && m->brow != 16 && m->brow != 32 && m->brow != 64 && m->brow != 128)
+        return SHFLBW_ERR_UNSUPPORTED;
     if (kernel == SHFLBW_KERNEL_SIMT && (N + 127) / 128 > 65535) return SHFLBW_ERR_UNSUPPORTED;   // column tiles ride in grid.y
     if (N % 8) return SHFLBW_ERR_UNSUPPORTED;                   // 16-byte rows of fp16
     const uintptr_t al = (uintptr_t)B | (uintptr_t)D | (uintptr_t)C;
@@ -338,6 +404,8 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
         if (rc != SHFLBW_OK) return rc;
         out->kernel = SHFLBW_KERNEL_TCGEN05;
         out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
+        out->gather = ch.gather;
+        if (ch.gather == shflbw::kGatherTma && (rc = encode_b_map(B, m->ncol, N, out->tmap_b)) != SHFLBW_OK) return rc;
         out->tiles_n = (N + ch.tokens - 1) / ch.tokens;
         out->num_items = out->tiles_n * out->num_row_blocks;
         const int sms = sm_count();
@@ -367,8 +435,10 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         shflbw::PanelParams p{};
         p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
-        p.wait_limit = shflbw::kWaitLimitCycles;
+        p.wait_limit = g_wait_limit; p.inject_from = g_inject_from; p.idx_limit = (unsigned)(st->K - 1);
         p.B = (const __half*)st->B; p.C = (const __half*)st->C; p.D = (__half*)st->D; p.N = st->N;
+        if (ch.gather != st->gather) return SHFLBW_ERR_INVALID_ARG;
+        if (st->gather == shflbw::kGatherTma) std::memcpy(p.tmap_b, st->tmap_b, sizeof p.tmap_b);
         p.num_items = st->num_items; p.tiles_n = st->tiles_n;
 #if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
         if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
@@ -465,60 +535,103 @@ static size_t unperm_smem_bytes(int F) {
     return (size_t)F * 2 * (1 + shflbw::kUnpermThreads / shflbw::unperm_threads_per_pos(F));
 }
 
-int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap,
-                       void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
-    if (!out) return SHFLBW_ERR_INVALID_ARG;
+// Launch plan of one NHWC SpConv call, without its scratch pointers: kernel choice, grid, and
+// the scratch each side needs.  Two plans exist.
+//   positions out   relayout -> panel kernel with tokens in TMEM lanes, writing [position][F] in
+//                   stored filter order -> (with a filter permutation) unpermute_filters.
+//   planes out      relayout -> panel kernel with the filters in TMEM lanes, writing the output
+//                   as planes [F][Ho][Wo][Bp] with plane = LOGICAL channel (the permutation is
+//                   the row index of its stores, free) -> chain_export_nhwc transposes the planes
+//                   to NHWC.  Used for V = 64 / 128 filters with enough non-zero columns per
+//                   block: one MMA per 16 columns covers the whole token tile.
+// SHFLBW_CONV_PLANES=0|1 forces the choice (tuning aid).
+int plan_conv(const shflbw_matrix* f, int B, int Hin, int Win, int stride, const void* ifmap, void* ofmap,
+              float alpha, int kernel, shflbw_spconv_state_t* out) {
     std::memset(out, 0, sizeof *out);
     if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
     ConvShape cs;
     int rc = check_conv_call(f, B, Hin, Win, stride, ifmap, ofmap, &cs);
     if (rc != SHFLBW_OK) return rc;
-    if (f->brow == 16 && kernel == SHFLBW_KERNEL_AUTO) kernel = SHFLBW_KERNEL_SIMT;   // as for SpMM
-    if (kernel != SHFLBW_KERNEL_SIMT && f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
+    if (kernel != SHFLBW_KERNEL_SIMT && f->brow != 16 && f->brow != 32 && f->brow != 64 && f->brow != 128)
+        return SHFLBW_ERR_UNSUPPORTED;
     const int Ho = cs.Ho, Wo = cs.Wo, Bp = cs.Bp;
-    const long long tokens = cs.tokens, staged_elems = cs.staged_elems;
+    const long long tokens = cs.tokens;
 
     out->B = B; out->Hin = Hin; out->Win = Win; out->C = f->C; out->F = f->F; out->R = f->R; out->S = f->S;
     out->stride = stride; out->Ho = Ho; out->Wo = Wo; out->V = f->brow; out->Bp = Bp;
     out->alpha = alpha; out->ifmap = ifmap; out->ofmap = ofmap;
     out->blk_ptr = f->d_kptr; out->blk_idx = f->d_kidx; out->blk_val = f->d_val;
     out->perm = f->d_perm; out->status_word = f->d_status;
-    if (kernel != SHFLBW_KERNEL_SIMT) {
-        // The panel kernel reads decoded column ids (channel in 16 bits, taps in 8 bits each).
-        if (!f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
-        out->blk_idx = f->d_kcrs;
-    }
     if (kernel == SHFLBW_KERNEL_SIMT) {
-        out->kernel = SHFLBW_KERNEL_SIMT;
         if ((f->F + 127) / 128 > 65535) return SHFLBW_ERR_UNSUPPORTED;
+        out->kernel = SHFLBW_KERNEL_SIMT;
         out->block_x = 128; out->grid_x = (unsigned)(B * Ho * Wo); out->grid_y = (f->F + 127) / 128;   // positions in grid.x
         out->init_success = 1;
         return SHFLBW_OK;
     }
+    // The panel kernel reads decoded column ids (channel in 16 bits, taps in 8 bits each).
+    if (!f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
+    out->blk_idx = f->d_kcrs;
+    const int row_blocks = f->F / f->brow;
+    const long long padded_cols = f->kptr.empty() ? 0 : f->kptr.back();
+
+    // planes out?
     PanelChoice ch;
-    rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
-    if (rc != SHFLBW_OK) return rc;
+    bool planes = false;
+    const size_t export_smem = (size_t)f->F * 16;
+    const bool planes_possible = (f->brow == 64 || f->brow == 128) && export_smem <= 227 * 1024 &&
+                                 (long long)f->F * tokens < (1ll << 32) - 1;
+    if (planes_possible) {
+        bool want = padded_cols >= 192ll * row_blocks;      // same rule as the chained layers: >= 3 stages per block
+        if (const char* e = getenv("SHFLBW_CONV_PLANES")) want = atoi(e) != 0;
+        if (want) {
+            rc = pick_panel<shflbw::kPanelConvChain>(f->brow, tokens, row_blocks, want ? (1ll << 40) : 0, &ch);
+            if (rc != SHFLBW_OK) return rc;
+            planes = ch.variant == 1;
+        }
+    }
+    if (planes) {
+        out->variant = 1;
+        out->staged_out_bytes = (size_t)f->F * (size_t)tokens * 2;
+        if (export_smem > 48 * 1024)
+            CK(cudaFuncSetAttribute((const void*)shflbw::chain_export_nhwc, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)export_smem));
+    } else {
+        rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, row_blocks, 0, &ch);
+        if (rc != SHFLBW_OK) return rc;
+        out->variant = 0;
+        if (f->row_permute) {
+            out->staged_out_bytes = (size_t)B * Ho * Wo * f->F * 2;
+            if (unperm_smem_bytes(f->F) > 227 * 1024 || f->F > 65536) return SHFLBW_ERR_UNSUPPORTED;
+            if (unperm_smem_bytes(f->F) > 48 * 1024)
+                CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)unperm_smem_bytes(f->F)));
+        }
+    }
     out->kernel = SHFLBW_KERNEL_TCGEN05;
-    out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw; out->variant = ch.variant;
+    out->tokens_per_cta = ch.tokens; out->stages = ch.stages; out->producer_warps = ch.pw;
     out->tiles_n = (int)((tokens + ch.tokens - 1) / ch.tokens);
-    out->num_items = out->tiles_n * (f->F / f->brow);
+    out->num_items = out->tiles_n * row_blocks;
     const int sms = sm_count();
     if (sms <= 0) return SHFLBW_ERR_CUDA;
     out->block_x = ch.threads;
     out->grid_x = persistent_grid(out->num_items, sms); out->grid_y = 1;
     out->shared_mem_size = ch.smem;
+    out->staged_in_bytes = (size_t)cs.staged_elems * 2;
+    return SHFLBW_OK;
+}
+
+int shflbw_spconv_init(shflbw_matrix_t* f, int B, int Hin, int Win, int stride, const void* ifmap,
+                       void* ofmap, float alpha, int kernel, shflbw_spconv_state_t* out) {
+    if (!out) return SHFLBW_ERR_INVALID_ARG;
+    int rc = plan_conv(f, B, Hin, Win, stride, ifmap, ofmap, alpha, kernel, out);
+    if (rc != SHFLBW_OK || out->kernel == SHFLBW_KERNEL_SIMT) return rc;
     // Scratch owned by the filter handle, grown on demand.
-    out->staged_in_bytes = (size_t)staged_elems * 2;
     if ((rc = grow_scratch(*f, &f->conv_in, &f->conv_in_bytes, out->staged_in_bytes)) != SHFLBW_OK) return rc;
     out->staged_in = f->conv_in;
-    if (f->row_permute) {
-        out->staged_out_bytes = (size_t)B * Ho * Wo * f->F * 2;
+    if (out->staged_out_bytes) {
         if ((rc = grow_scratch(*f, &f->conv_out, &f->conv_out_bytes, out->staged_out_bytes)) != SHFLBW_OK) return rc;
         out->staged_out = f->conv_out;
-        if (unperm_smem_bytes(f->F) > 227 * 1024 || f->F > 65536) return SHFLBW_ERR_UNSUPPORTED;
-        if (unperm_smem_bytes(f->F) > 48 * 1024)
-            CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)unperm_smem_bytes(f->F)));
     }
     out->init_success = 1;
     return SHFLBW_OK;
@@ -535,10 +648,11 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
         CK(cudaGetLastError());
         return SHFLBW_OK;
     }
+    const bool planes = !st->chain && st->variant == 1;     // NHWC call computed as planes, then transposed
     PanelChoice ch;
-    const bool ok_kernel = !st->chain        ? lookup<shflbw::kPanelConv>(st->V, st->tokens_per_cta, &ch)
-                           : st->variant == 1 ? lookup<shflbw::kPanelConvChainRows>(st->V, st->tokens_per_cta, &ch)
-                                              : lookup<shflbw::kPanelConvChain>(st->V, st->tokens_per_cta, &ch);
+    const bool ok_kernel = (!st->chain && !planes) ? lookup<shflbw::kPanelConv>(st->V, st->tokens_per_cta, &ch)
+                           : st->variant == 1      ? lookup<shflbw::kPanelConvChainRows>(st->V, st->tokens_per_cta, &ch)
+                                                   : lookup<shflbw::kPanelConvChain>(st->V, st->tokens_per_cta, &ch);
     if (!ok_kernel) return SHFLBW_ERR_INVALID_ARG;
     // 1. NHWC -> channel-major, batch-innermost staging with a zero halo (chained layers get
     //    their input in that layout already).
@@ -550,7 +664,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     shflbw::PanelParams p{};
     p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
     p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = 0.f;
-    p.wait_limit = shflbw::kWaitLimitCycles;
+    p.wait_limit = g_wait_limit; p.inject_from = g_inject_from;
     p.N = st->Ho * st->Wo * st->Bp;
     p.Xs = (const __half*)(st->chain ? st->ifmap : st->staged_in);
     p.out = (__half*)(st->staged_out ? st->staged_out : st->ofmap);
@@ -559,7 +673,11 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
         const int OHp = st->Ho + st->out_R - 1;
         p.OWp = st->Wo + st->out_S - 1; p.oph = st->out_R / 2; p.opw = st->out_S / 2;
         p.out_plane = OHp * p.OWp * st->Bp; p.relu = st->relu;
+    } else if (planes) {
+        p.OWp = st->Wo; p.oph = 0; p.opw = 0; p.out_plane = st->Ho * st->Wo * st->Bp;
+        p.out_logical = 1;                                   // plane index = logical channel
     }
+    p.idx_limit = (unsigned)((((long long)st->C - 1) * Hp * Wp + (long long)(st->R - 1) * Wp + (st->S - 1)) * st->Bp);
     p.Bn = st->B; p.Bp = st->Bp; p.Hp = Hp; p.Wp = Wp; p.Cin = st->C; p.F = st->F;
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
     p.num_items = st->num_items; p.tiles_n = st->tiles_n;
@@ -567,9 +685,14 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
     if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
 #endif
-    ch.fn<<<dim3(st->grid_x, st->grid_y), st->block_x, st->shared_mem_size, s>>>(p);
-    // 3. inverse filter permutation.
-    if (st->staged_out) {
+    ch.fn<<<dim3(st->grid_x, st->grid_y), ch.threads, ch.smem, s>>>(p);
+    // 3. back to NHWC in logical channel order.
+    if (planes) {
+        const long long blocks = (long long)st->Ho * st->Wo * (st->Bp / 8);
+        shflbw::chain_export_nhwc<<<(unsigned)blocks, 256, (size_t)st->F * 16, s>>>(
+            (const __half*)st->staged_out, (__half*)st->ofmap, nullptr, st->B, st->Bp, st->Ho, st->Wo, st->Ho, st->Wo,
+            0, 0, st->F);
+    } else if (st->staged_out) {
         const int num_pos = st->B * st->Ho * st->Wo;
         const int per_block = shflbw::kUnpermThreads / shflbw::unperm_threads_per_pos(st->F);
         int blocks = (num_pos + per_block - 1) / per_block;
@@ -752,21 +875,16 @@ int shflbw_spconv_chain_set_residual(shflbw_matrix_t* f, shflbw_spconv_state_t* 
 
 int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, int Win, int stride,
                                       const void* ifmap, void* ofmap, float alpha, void* stream) {
-    // Same argument and 32-bit range checks as shflbw_spconv_init: with an unpermuted filter the
-    // output goes straight to ofmap, so the scratch capacity alone would not bound its offsets.
-    ConvShape cs;
-    int rc = check_conv_call(f, B, Hin, Win, stride, ifmap, ofmap, &cs);
+    // Same argument checks, 32-bit range checks and launch plan as shflbw_spconv_init (with an
+    // unpermuted filter the output can bypass the array, so its capacity alone would not bound
+    // the output offsets); only the scratch comes from somewhere else.
+    shflbw_spconv_state_t st;
+    int rc = plan_conv(f, B, Hin, Win, stride, ifmap, ofmap, alpha, SHFLBW_KERNEL_TCGEN05, &st);
     if (rc != SHFLBW_OK) return rc;
-    if (f->brow != 32 && f->brow != 64 && f->brow != 128) return SHFLBW_ERR_UNSUPPORTED;
-    if (!f->d_kcrs) return SHFLBW_ERR_UNSUPPORTED;
-    const int Ho = cs.Ho, Wo = cs.Wo, Bp = cs.Bp;
-    const long long tokens = cs.tokens;
 
-    // Capacity check first: nothing is launched when the shape does not fit.  (Both terms are
-    // below 2^33 after the checks above.)
+    // Capacity check first: nothing is launched when the shape does not fit.
     auto up256 = [](unsigned long long v) { return (v + 255ull) / 256ull * 256ull; };
-    const unsigned long long in_bytes = up256(2ull * (unsigned long long)cs.staged_elems);
-    const unsigned long long out_bytes = f->row_permute ? up256(2ull * B * Ho * Wo * f->F) : 0ull;
+    const unsigned long long in_bytes = up256(st.staged_in_bytes), out_bytes = up256(st.staged_out_bytes);
     if (in_bytes + out_bytes > (unsigned long long)SHFLBW_STATIC_SCRATCH_BYTES) {
         snprintf(g_cuda_err, sizeof g_cuda_err,
                  "static scratch: this shape needs %llu bytes, the built-in array holds %u",
@@ -785,34 +903,8 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
         g_static_scratch_addr[dev] = ptr;
     }
     unsigned char* scratch = (unsigned char*)g_static_scratch_addr[dev];
-
-    // Same launch plan as shflbw_spconv_init, with the scratch pointers taken from the array.
-    shflbw_spconv_state_t st;
-    std::memset(&st, 0, sizeof st);
-    PanelChoice ch;
-    rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, f->F / f->brow, 0, &ch);
-    if (rc != SHFLBW_OK) return rc;
-    const int sms = sm_count();
-    if (sms <= 0) return SHFLBW_ERR_CUDA;
-    st.B = B; st.Hin = Hin; st.Win = Win; st.C = f->C; st.F = f->F; st.R = f->R; st.S = f->S;
-    st.stride = stride; st.Ho = Ho; st.Wo = Wo; st.V = f->brow; st.Bp = Bp;
-    st.kernel = SHFLBW_KERNEL_TCGEN05;
-    st.tokens_per_cta = ch.tokens; st.stages = ch.stages; st.producer_warps = ch.pw; st.variant = ch.variant;
-    st.tiles_n = (int)((tokens + ch.tokens - 1) / ch.tokens);
-    st.num_items = st.tiles_n * (f->F / f->brow);
-    st.block_x = ch.threads; st.grid_x = persistent_grid(st.num_items, sms); st.grid_y = 1;
-    st.shared_mem_size = ch.smem;
-    st.alpha = alpha; st.ifmap = ifmap; st.ofmap = ofmap;
-    st.staged_in = scratch; st.staged_in_bytes = (size_t)in_bytes;
-    if (f->row_permute) {
-        st.staged_out = scratch + in_bytes; st.staged_out_bytes = (size_t)out_bytes;
-        if (unperm_smem_bytes(f->F) > 227 * 1024 || f->F > 65536) return SHFLBW_ERR_UNSUPPORTED;
-        if (unperm_smem_bytes(f->F) > 48 * 1024)
-            CK(cudaFuncSetAttribute((const void*)shflbw::unpermute_filters,
-                                    cudaFuncAttributeMaxDynamicSharedMemorySize, (int)unperm_smem_bytes(f->F)));
-    }
-    st.blk_ptr = f->d_kptr; st.blk_idx = f->d_kcrs; st.blk_val = f->d_val;
-    st.perm = f->d_perm; st.status_word = f->d_status;
+    st.staged_in = scratch;
+    if (st.staged_out_bytes) st.staged_out = scratch + in_bytes;
     st.init_success = 1;
     return shflbw_spconv_exec(&st, stream);
 }

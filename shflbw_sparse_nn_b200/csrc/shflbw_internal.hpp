@@ -14,9 +14,9 @@
 constexpr int kShflbwKPad = 16;
 
 // Kernel image of the value panels.  Element (padded row r, row-in-block m) lives at
-// kval_index(V, r, m).  For V = 32 / 64 / 128 every group of 8 rows is stored in exactly the
+// kval_index(V, r, m).  For V = 16 / 32 / 64 / 128 every group of 8 rows is stored in exactly the
 // byte order the tensor-core operand tile has in shared memory (16-byte chunks XOR-swizzled by
-// the row, 128-byte or 64-byte swizzle atoms), so a pipeline stage of the panel is ONE
+// the row; 128-, 64- or 32-byte swizzle atoms), so a pipeline stage of the panel is ONE
 // contiguous run that a bulk copy drops into place.  Other V: plain row-major.
 #if defined(__CUDACC__)
 #define SHFLBW_HD __host__ __device__
@@ -29,6 +29,7 @@ SHFLBW_HD inline size_t kval_index(int V, size_t r, int m) {
     if (V == 64) return grp + r7 * 64 + (size_t)((c ^ (int)r7) << 3) + e;
     if (V == 128) return grp + (size_t)(c >> 3) * 512 + r7 * 64 + (size_t)(((c & 7) ^ (int)r7) << 3) + e;
     if (V == 32) return grp + r7 * 32 + (size_t)((c ^ (int)((r7 >> 1) & 3)) << 3) + e;
+    if (V == 16) return grp + r7 * 16 + (size_t)((c ^ (int)((r7 >> 2) & 1)) << 3) + e;
     return r * (size_t)V + m;
 }
 

@@ -47,19 +47,21 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
 // NOT inlined, so the hot loops of the kernel stay short and straight (the kernels proved
 // sensitive to instruction fetch: a taken branch to a cold line cost ~150 clk).  Between
 // polls the thread sleeps `backoff_ns` so waiting warps leave the issue slots to the others.
+// `heed_abort = false` is for the clean-up wait of the abort path itself (the flag is already up
+// there); `code` 0 records nothing.
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
                                             int* status_word, int code, long long limit_cycles,
-                                            uint32_t backoff_ns) {
+                                            uint32_t backoff_ns, bool heed_abort) {
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (true) {
         if (backoff_ns) __nanosleep(backoff_ns);
         if (mbar_test(bar, parity)) return true;
         if ((++spins & 0xf) == 0) {
-            if (*cta_abort) return false;
+            if (heed_abort && *cta_abort) return false;
             if (clock64() - t0 > limit_cycles) {
                 *cta_abort = 1;
-                atomicCAS(status_word, 0, code);
+                if (code) atomicCAS(status_word, 0, code);
                 return false;
             }
         }
@@ -67,13 +69,13 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
 }
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* cta_abort,
                                                   int* status_word, int code, long long limit_cycles,
-                                                  uint32_t backoff_ns = 40) {
+                                                  uint32_t backoff_ns = 40, bool heed_abort = true) {
     // Most waits in the kernels are short (a few hundred clocks): poll a handful of times in
     // line before paying for the call and the first sleep of the slow path.
 #pragma unroll 1
     for (int i = 0; i < 12; ++i)
         if (mbar_test(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, cta_abort, status_word, code, limit_cycles, backoff_ns);
+    return mbar_wait_slow(bar, parity, cta_abort, status_word, code, limit_cycles, backoff_ns, heed_abort);
 }
 
 // ----------------------------------------------------------------- bulk copy ----
@@ -86,6 +88,26 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+// One arrival plus `bytes` added to the pending transaction count, in one operation.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Subtracts `bytes` from the pending transaction count by hand (tuning builds that skip a copy).
+__device__ __forceinline__ void mbar_complete_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.complete_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// TMA tile::gather4: rows r0..r3 of a 2-D tensor (tensor map box = W columns x 1 row), columns
+// [col, col + W), land as 4 consecutive rows of W elements at dst (swizzled as the map says) and
+// complete 4*W*elemsize bytes on the barrier.  Columns or rows outside the tensor read as zero.
+// The map must describe memory of THIS GPU; this is the plain .shared::cta form, no multicast.
+__device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const void* tmap, int col, int r0, int r1, int r2, int r3,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5, %6}], [%7];"
+        ::"r"(dst_smem), "l"(tmap), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_u32(bar))
+        : "memory");
 }
 
 // ------------------------------------------------------------------ cp.async ----
@@ -177,6 +199,16 @@ __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)
         : "r"(taddr)
         : "memory");
 }
+// TMEM -> registers: the warp's 32 lanes x 16 consecutive fp32 columns.
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
 // TMEM -> registers: the warp's 32 lanes x 8 consecutive fp32 columns.
 __device__ __forceinline__ void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8]) {
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
@@ -196,8 +228,9 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // i.e. one K row is a 128-byte line (64 fp16 along MN), eight K rows form a 1024-byte atom,
 // atoms repeat along MN every LBO bytes and along K every SBO bytes, and the 16-byte chunk
 // index inside a line is XORed with (row % 8).  With 64-byte swizzle the line is 64 bytes
-// (32 fp16), the atom 512 bytes, and the chunk index is XORed with ((row / 2) % 4).
-constexpr uint64_t kSwizzle128B = 2, kSwizzle64B = 4;
+// (32 fp16), the atom 512 bytes, and the chunk index is XORed with ((row / 2) % 4); with 32-byte
+// swizzle the line is 32 bytes (16 fp16), the atom 256 bytes, and the XOR term is ((row / 4) % 2).
+constexpr uint64_t kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6;
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
                                                    uint32_t sbo_bytes, uint64_t swizzle) {
     return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16) |

@@ -39,7 +39,7 @@ def test_state_structs_match_the_header_field_order():
             if not decl:
                 continue
             for part in decl.split(","):
-                names.append(re.sub(r"[\*\s]", " ", part).split()[-1])
+                names.append(re.sub(r"[\*\s]", " ", re.sub(r"\[.*?\]", "", part)).split()[-1])   # arrays: name without [n]
         assert names == [f[0] for f in cls._fields_], struct
 
 

@@ -59,16 +59,18 @@ def test_batch_not_multiple_of_8_and_1x1(Bn):
 
 
 @pytest.mark.parametrize("tokens", [128, 256])
-def test_reference_test_shape_int9(tokens):
-    """The reference's conv test case (n,h,w,c,f,r,s,stride) = (128,14,14,256,256,3,3,1), d=0.1,
-    seed 2021, integer inputs, its exact acceptance rule; run at batch 16 to bound CPU time,
-    and with the filter permutation ON (the reference never tests that path)."""
+@pytest.mark.parametrize("stride", [1, 2])
+def test_reference_test_shape_int9(tokens, stride):
+    """The reference's conv test cases (n,h,w,c,f,r,s) = (128,14,14,256,256,3,3) at stride 1 and 2
+    (test/test.spconv.blockwise.cu:10-15), d=0.1, seed 2021, integer inputs, its exact acceptance
+    rule; run at batch 16 to bound CPU time, and with the filter permutation ON (the reference
+    never tests that path).  Stride 2 follows the standard definition Ho = ceil(Hin / 2)."""
     ctypes.CDLL(None).srand(3)
     f = sb.BlockwiseSpFilter().init_random(256, 3, 3, 256, 64, 1, 0.1, True, 2021, values="int9")
     x = np.random.default_rng(5).integers(-4, 5, (16, 14, 14, 256)).astype(np.float16)
-    O, op = run_spconv(f, 16, 14, 14, 1, x, tokens=tokens)
-    assert op._state.tokens_per_cta == tokens
-    assert oa.ref_rule_violations(O, _oracle(f, 16, 14, 14, 1, x)) == 0
+    O, op = run_spconv(f, 16, 14, 14, stride, x, tokens=tokens)
+    assert op._state.tokens_per_cta == tokens and O.shape == (16, 14 // stride, 14 // stride, 256)
+    assert oa.ref_rule_violations(O, _oracle(f, 16, 14, 14, stride, x)) == 0
 
 
 def test_simt_cross_check_kernel_matches_oracle():
@@ -113,12 +115,29 @@ def test_host_buffer_call_equals_device_call():
     assert np.array_equal(O_host.view(np.uint16), O_dev.view(np.uint16))
 
 
-def test_filter_block_height_16_runs_on_the_cuda_core_kernel():
-    f = sb.BlockwiseSpFilter().init_random(64, 3, 3, 16, 16, 1, 0.3, True, 2, values="uniform")
-    x = sb.uniform_half(716, 4 * 6 * 5 * 16).reshape(4, 6, 5, 16)
-    O, op = run_spconv(f, 4, 6, 5, 1, x)
-    assert op._state.kernel == sb.KERNEL_SIMT and op.launches_per_exec == 1
-    assert_close_fp16(O, _oracle(f, 4, 6, 5, 1, x), what="conv V=16")
+@pytest.mark.parametrize("permute", [False, True])
+def test_filter_block_height_16_on_the_tensor_cores(permute):
+    """V = 16 (the reference instantiates it, spconv/blockwise_library.cu:16-32) on the tcgen05
+    kernel, at a ResNet-50 shape with batch 32 (more than 65535 output positions)."""
+    Bn, H, W, Cc, F = 32, 56, 56, 64, 64
+    f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, 16, 1, 0.2, permute, 2, values="uniform")
+    x = sb.uniform_half(716, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    O, op = run_spconv(f, Bn, H, W, 1, x)
+    assert op._state.kernel == sb.KERNEL_TCGEN05 and op._state.tokens_per_cta == 128
+    assert_close_fp16(O, _oracle(f, Bn, H, W, 1, x), what="conv V=16")
+    f2 = sb.BlockwiseSpFilter().init_random(64, 3, 3, 16, 16, 1, 0.3, True, 2, values="uniform")
+    x2 = sb.uniform_half(717, 4 * 6 * 5 * 16).reshape(4, 6, 5, 16)
+    O2, _ = run_spconv(f2, 4, 6, 5, 2, x2)
+    assert_close_fp16(O2, _oracle(f2, 4, 6, 5, 2, x2), what="conv V=16 small, stride 2")
+
+
+def test_plain_kernel_takes_more_than_65535_output_positions():
+    Bn, H, W, Cc, F = 24, 56, 56, 16, 32          # 75264 positions
+    f = sb.BlockwiseSpFilter().init_random(F, 1, 1, Cc, 32, 1, 0.5, True, 4, values="uniform")
+    x = sb.uniform_half(718, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    O, op = run_spconv(f, Bn, H, W, 1, x, kernel=sb.KERNEL_SIMT)
+    assert op._state.kernel == sb.KERNEL_SIMT
+    assert_close_fp16(O, _oracle(f, Bn, H, W, 1, x), what="plain conv kernel, 75264 positions")
 
 
 def test_states_stay_valid_when_a_later_init_needs_larger_scratch():

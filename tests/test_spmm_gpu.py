@@ -169,16 +169,37 @@ def test_meta_image_equals_reference_transform_and_sync_device():
     assert np.array_equal(m.meta_h, r.meta_image())
 
 
-def test_row_block_height_16_runs_on_the_cuda_core_kernel():
-    """V = 16 (instantiated by the reference, spmm/blockwise_library.cu:15-31) is served by the
-    plain CUDA-core kernel under KERNEL_AUTO; asking for the tensor-core kernel is refused."""
+@pytest.mark.parametrize("permute", [False, True])
+def test_row_block_height_16_reference_shape_on_the_tensor_cores(permute):
+    """V = 16 (instantiated by the reference, spmm/blockwise_library.cu:15-31) runs on the tcgen05
+    kernel (UMMA M = 128 tokens, N = 16): the reference's own test case
+    (m,n,k,d,seed) = (1024,960,1024,0.1,2021), integer inputs, its exact acceptance rule
+    (test/test.spmm.blockwise.cu:10-14, test_util.spmm.h:18)."""
+    ctypes.CDLL(None).srand(16 + permute)
+    m = sb.BlockwiseSpMatrix().init_random(1024, 1024, 16, 1, 0.1, permute, 2021, values="int9")
+    B = np.random.default_rng(16).integers(-4, 5, (1024, 960)).astype(np.float16)
+    D, op = run_spmm(m, 960, B)
+    assert op._state.kernel == sb.KERNEL_TCGEN05 and op._state.tokens_per_cta == 128
+    assert oa.ref_rule_violations(D, _oracle(m, 960, B)) == 0
+
+
+@pytest.mark.parametrize("N", [8, 136, 520])
+def test_row_block_height_16_residue_alpha_beta_and_large_row_counts(N):
+    """V = 16 with uniform data, a ragged dense width, alpha / beta, and more than 65535 rows."""
     m = sb.BlockwiseSpMatrix().init_random(256, 384, 16, 1, 0.2, True, 2021, values="uniform")
-    B = sb.uniform_half(616, 384 * 128).reshape(384, 128)
-    D, op = run_spmm(m, 128, B)
-    assert op._state.kernel == sb.KERNEL_SIMT
-    assert_close_fp16(D, _oracle(m, 128, B), what="V=16")
-    with pytest.raises(sb.ShflbwError):
-        run_spmm(m, 128, B, kernel=sb.KERNEL_TCGEN05)
+    B = sb.uniform_half(616, 384 * N).reshape(384, N)
+    Cm = sb.uniform_half(617, 256 * N).reshape(256, N)
+    D, op = run_spmm(m, N, B, 0.5, Cm, 2.0)
+    assert op._state.kernel == sb.KERNEL_TCGEN05
+    assert_close_fp16(D, _oracle(m, N, B, 0.5, Cm, 2.0), what=f"V=16 N={N}")
+    if N == 8:   # many rows: 70000 > 65535 on both kernels (the plain kernel indexes rows in grid.x)
+        big = sb.BlockwiseSpMatrix().init_random(70000 // 16 * 16, 64, 16, 1, 0.25, True, 5, values="uniform")
+        Bb = sb.uniform_half(6, 64 * 8).reshape(64, 8)
+        D1, _ = run_spmm(big, 8, Bb)
+        D2, op2 = run_spmm(big, 8, Bb, kernel=sb.KERNEL_SIMT)
+        assert op2._state.kernel == sb.KERNEL_SIMT
+        assert_close_fp16(D1, _oracle(big, 8, Bb), what="V=16, 70000 rows")
+        assert_close_fp16(D2, D1.astype(np.float32), what="plain kernel, 70000 rows")
 
 
 @pytest.mark.parametrize("V", [64, 128])
