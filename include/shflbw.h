@@ -204,6 +204,13 @@ int shflbw_matrix_device_status(const shflbw_matrix_t* m);
 int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
                      const void* C_host, float beta, void* D_host);
 
+/* Measurement aid for shflbw_spmm_host: moves the same bytes of B in and of D out through the
+ * same staging buffers, streams and events, in the same chunks, WITHOUT launching the kernel --
+ * the time of the link alone, which bounds the host-buffer call from below.  contiguous != 0
+ * moves every chunk as one contiguous block of the same size instead of a strided column slice
+ * (what the strided form costs).  D_host receives staging-buffer contents, not a result. */
+int shflbw_spmm_host_copies_only(shflbw_matrix_t* m, int N, const void* B_host, void* D_host, int contiguous);
+
 /* ----------------------------------------------------------------------- SpConv ---- */
 
 /* Replaces SpconvBlockwiseOpState (block_sparse/spconv/blockwise_op.h:6-17). */

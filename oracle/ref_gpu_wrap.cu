@@ -123,4 +123,44 @@ int ref_gpu_spconv(int cfg, int Bn, int H, int W, int C, int F, int R, int S, in
     return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
 
+// L2-cold variants: `nb` buffer pairs are rotated (state i % nb per launch) so that, with the
+// pairs larger than L2 in aggregate, every launch reads its dense operand from HBM -- the same
+// protocol the product kernels are timed with.  Only timing; run ref_gpu_spmm / ref_gpu_spconv
+// first to check results.
+int ref_gpu_spmm_rotating(int cfg, int M, int K, int N, int brow, int nnzb, const int* indptr,
+                          const int* indices, const uint16_t* values, const int* perm, void** B_dev,
+                          void** D_dev, int nb, int warmup, int repeat, float* ms) {
+    if (cfg < 0 || cfg >= ref_gpu_num_spmm_configs() || kSpmm[cfg].V != brow || nb < 1 || nb > 64) return 1;
+    BlockwiseSpMatrix<half> m;
+    fill(m, M, K, brow, nnzb, indptr, indices, values, perm);
+    m.transform_and_sync_device();
+    std::vector<SpmmBlockwiseOpState> st;
+    for (int i = 0; i < nb; ++i) {
+        st.push_back(kSpmm[cfg].init(m, N, (half*)B_dev[i], (half*)D_dev[i]));
+        if (!st.back().initSuccess) return 2;
+    }
+    int i = 0;
+    *ms = time_launches([&] { kSpmm[cfg].exec(st[i], 0); i = (i + 1) % nb; }, warmup, repeat);
+    return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
+int ref_gpu_spconv_rotating(int cfg, int Bn, int H, int W, int C, int F, int R, int S, int stride, int brow,
+                            int nnzb, const int* indptr, const int* indices, const uint16_t* values,
+                            const int* perm, void** ifmap_dev, void** ofmap_dev, int nb, int warmup, int repeat,
+                            float* ms) {
+    if (cfg < 0 || cfg >= ref_gpu_num_conv_configs() || kConv[cfg].V != brow || nb < 1 || nb > 64) return 1;
+    BlockwiseSpFilter<half> f;
+    fill(f, F, R * S * C, brow, nnzb, indptr, indices, values, perm);
+    f.F = F; f.C = C; f.R = R; f.S = S;
+    f.transform_and_sync_device();
+    std::vector<SpconvBlockwiseOpState> st;
+    for (int i = 0; i < nb; ++i) {
+        st.push_back(kConv[cfg].init(f, Bn, H, W, stride, (half*)ifmap_dev[i], (half*)ofmap_dev[i]));
+        if (!st.back().initSuccess) return 2;
+    }
+    int i = 0;
+    *ms = time_launches([&] { kConv[cfg].exec(st[i], 0); i = (i + 1) % nb; }, warmup, repeat);
+    return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}
+
 }  // extern "C"

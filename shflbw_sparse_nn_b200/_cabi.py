@@ -99,6 +99,7 @@ _PROTOS = {
                                    C.c_int, C.POINTER(SpmmState)]),
     "shflbw_spmm_exec": (C.c_int, [C.POINTER(SpmmState), C.c_void_p]),
     "shflbw_spmm_host": (C.c_int, [_H, C.c_int, C.c_void_p, C.c_float, C.c_void_p, C.c_float, C.c_void_p]),
+    "shflbw_spmm_host_copies_only": (C.c_int, [_H, C.c_int, C.c_void_p, C.c_void_p, C.c_int]),
     "shflbw_spmm_launches_per_exec": (C.c_int, [C.POINTER(SpmmState)]),
     "shflbw_spconv_init": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                      C.c_float, C.c_int, C.POINTER(SpconvState)]),

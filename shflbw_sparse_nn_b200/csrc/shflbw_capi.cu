@@ -201,11 +201,31 @@ unsigned persistent_grid(int num_items, int sms) {
     return (unsigned)(g > need ? g : need);
 }
 
+constexpr int kMaxDevices = 64;
+
+// SM count of the current device, looked up once per device.
 int sm_count() {
+    static int cached[kMaxDevices] = {};
     int dev = 0, n = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMaxDevices && cached[dev] > 0) return cached[dev];
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (dev >= 0 && dev < kMaxDevices) cached[dev] = n;
     return n;
+}
+
+// Opt a panel kernel in to its dynamic shared memory once per (device, kernel): the host-buffer
+// calls initialise an op per chunk, and the attribute call is not free.
+int allow_smem(PanelKernel fn, size_t bytes) {
+    struct Done { const void* fn; int dev; };
+    static Done done[256];
+    static int n_done = 0;
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    for (int i = 0; i < n_done; ++i) if (done[i].fn == (const void*)fn && done[i].dev == dev) return SHFLBW_OK;
+    CK(cudaFuncSetAttribute((const void*)fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    if (n_done < 256) done[n_done++] = {(const void*)fn, dev};
+    return SHFLBW_OK;
 }
 
 // Tile selection.  A 256-token work item halves the value-panel traffic per token and is
@@ -240,8 +260,7 @@ int pick_panel(int V, long long n_tokens, int row_blocks, long long padded_cols,
     }
     if (!swapped && !lookup<MODE>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
     out->variant = swapped ? 1 : 0;
-    CK(cudaFuncSetAttribute((const void*)out->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)out->smem));
-    return SHFLBW_OK;
+    return allow_smem(out->fn, out->smem);
 }
 
 // Argument and range checks shared by every NHWC SpConv entry point.  The kernels index the
@@ -282,7 +301,6 @@ int check_kernel_arg(int kernel) {
 static __device__ __align__(256) unsigned char g_static_scratch[SHFLBW_STATIC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
 void* g_static_scratch_addr[kMaxDevices] = {};  // device address of the array, per device
 }  // namespace
 
@@ -458,8 +476,11 @@ int shflbw_spmm_launches_per_exec(const shflbw_spmm_state_t* st) { return st && 
 // instead of their sum plus the kernel.  (Overlap needs page-locked host buffers; pageable ones
 // work, the copies then serialise.)  A chunk is staged contiguously ([K][w] / [M][w]) by a strided
 // 2-D copy, so the kernels run unchanged on dense chunks.
-int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha, const void* C_host,
-                     float beta, void* D_host) {
+// mode 0: the real call.  1: the same copies through the same streams and events, no kernel
+// (what the link alone costs).  2: as 1, but every chunk moves as one contiguous block of the
+// same size (what the strided form of the chunk copies costs on top).
+static int spmm_host_impl(shflbw_matrix_t* m, int N, const void* B_host, float alpha, const void* C_host,
+                          float beta, void* D_host, int mode) {
     if (!m || !B_host || !D_host || N <= 0) return SHFLBW_ERR_INVALID_ARG;
     if (beta != 0.f && !C_host) return SHFLBW_ERR_INVALID_ARG;
     if (N % 8) return SHFLBW_ERR_UNSUPPORTED;
@@ -495,6 +516,10 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
         __half* dB = (__half*)m->stage_in + (size_t)m->ncol * c0;
         __half* dD = (__half*)m->stage_out + (size_t)m->nrow * c0;
         __half* dC = beta != 0.f ? (__half*)m->stage_c + (size_t)m->nrow * c0 : nullptr;
+        if (mode == 2)
+            CKH(cudaMemcpyAsync(dB, (const __half*)B_host + (size_t)m->ncol * c0, (size_t)wi * 2 * m->ncol,
+                                cudaMemcpyHostToDevice, s_in));
+        else
         CKH(cudaMemcpy2DAsync(dB, (size_t)wi * 2, (const __half*)B_host + c0, pitch_h, (size_t)wi * 2, m->ncol,
                               cudaMemcpyHostToDevice, s_in));
         if (dC)
@@ -502,12 +527,18 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
                                   cudaMemcpyHostToDevice, s_in));
         CKH(cudaEventRecord(e_in[i], s_in));
         CKH(cudaStreamWaitEvent(s_k, e_in[i], 0));
-        shflbw_spmm_state_t st;
-        rc = shflbw_spmm_init(m, wi, dB, alpha, dC, beta, dD, SHFLBW_KERNEL_AUTO, &st);
-        if (rc == SHFLBW_OK) rc = shflbw_spmm_exec(&st, s_k);
-        if (rc != SHFLBW_OK) return fail(rc);
+        if (mode == 0) {
+            shflbw_spmm_state_t st;
+            rc = shflbw_spmm_init(m, wi, dB, alpha, dC, beta, dD, SHFLBW_KERNEL_AUTO, &st);
+            if (rc == SHFLBW_OK) rc = shflbw_spmm_exec(&st, s_k);
+            if (rc != SHFLBW_OK) return fail(rc);
+        }
         CKH(cudaEventRecord(e_k[i], s_k));
         CKH(cudaStreamWaitEvent(s_out, e_k[i], 0));
+        if (mode == 2)
+            CKH(cudaMemcpyAsync((__half*)D_host + (size_t)m->nrow * c0, dD, (size_t)wi * 2 * m->nrow,
+                                cudaMemcpyDeviceToHost, s_out));
+        else
         CKH(cudaMemcpy2DAsync((__half*)D_host + c0, pitch_h, dD, (size_t)wi * 2, (size_t)wi * 2, m->nrow,
                               cudaMemcpyDeviceToHost, s_out));
     }
@@ -516,6 +547,15 @@ int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha,
     CKH(cudaStreamSynchronize(s_in));
 #undef CKH
     return SHFLBW_OK;
+}
+
+int shflbw_spmm_host(shflbw_matrix_t* m, int N, const void* B_host, float alpha, const void* C_host,
+                     float beta, void* D_host) {
+    return spmm_host_impl(m, N, B_host, alpha, C_host, beta, D_host, 0);
+}
+
+int shflbw_spmm_host_copies_only(shflbw_matrix_t* m, int N, const void* B_host, void* D_host, int contiguous) {
+    return spmm_host_impl(m, N, B_host, 1.0f, nullptr, 0.0f, D_host, contiguous ? 2 : 1);
 }
 
 // ---------------------------------------------------------------------------- SpConv --

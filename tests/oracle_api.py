@@ -240,6 +240,9 @@ def ref_gpu():
         l.ref_gpu_conv_config_name.restype = C.c_char_p
         l.ref_gpu_spmm.argtypes = [C.c_int] * 6 + [C.c_void_p] * 6 + [C.c_int, C.c_int, C.POINTER(C.c_float)]
         l.ref_gpu_spconv.argtypes = [C.c_int] * 11 + [C.c_void_p] * 6 + [C.c_int, C.c_int, C.POINTER(C.c_float)]
+        if hasattr(l, "ref_gpu_spmm_rotating"):
+            l.ref_gpu_spmm_rotating.argtypes = [C.c_int] * 6 + [C.c_void_p] * 6 + [C.c_int] * 3 + [C.POINTER(C.c_float)]
+            l.ref_gpu_spconv_rotating.argtypes = [C.c_int] * 11 + [C.c_void_p] * 6 + [C.c_int] * 3 + [C.POINTER(C.c_float)]
         _ref_gpu = l
     return _ref_gpu
 
@@ -270,4 +273,27 @@ def ref_gpu_spconv(cfg, Bn, H, W, Cc, F, R, S, stride, brow, indptr, indices, va
     v = np.ascontiguousarray(values).view(np.uint16)
     rc = ref_gpu().ref_gpu_spconv(cfg, Bn, H, W, Cc, F, R, S, stride, brow, int(indices.size), _P(indptr),
                                   _P(indices), _P(v), _P(perm), in_ptr, out_ptr, warmup, repeat, C.byref(ms))
+    return rc, ms.value
+
+
+def _ptr_array(ptrs):
+    return (C.c_void_p * len(ptrs))(*ptrs)
+
+
+def ref_gpu_spmm_rotating(cfg, M, K, N, brow, indptr, indices, values, perm, B_ptrs, D_ptrs, warmup, repeat):
+    """Mean time (ms) of the reference SpMM kernel over `repeat` launches that rotate the buffer pairs."""
+    ms = C.c_float(0)
+    v = np.ascontiguousarray(values).view(np.uint16)
+    rc = ref_gpu().ref_gpu_spmm_rotating(cfg, M, K, N, brow, int(indices.size), _P(indptr), _P(indices), _P(v), _P(perm),
+                                         _ptr_array(B_ptrs), _ptr_array(D_ptrs), len(B_ptrs), warmup, repeat, C.byref(ms))
+    return rc, ms.value
+
+
+def ref_gpu_spconv_rotating(cfg, Bn, H, W, Cc, F, R, S, stride, brow, indptr, indices, values, perm, in_ptrs, out_ptrs,
+                            warmup, repeat):
+    ms = C.c_float(0)
+    v = np.ascontiguousarray(values).view(np.uint16)
+    rc = ref_gpu().ref_gpu_spconv_rotating(cfg, Bn, H, W, Cc, F, R, S, stride, brow, int(indices.size), _P(indptr),
+                                           _P(indices), _P(v), _P(perm), _ptr_array(in_ptrs), _ptr_array(out_ptrs),
+                                           len(in_ptrs), warmup, repeat, C.byref(ms))
     return rc, ms.value
