@@ -341,6 +341,38 @@ int shflbw_spconv_chain_set_residual(shflbw_matrix_t* filter, shflbw_spconv_stat
 int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* filter, int B, int Hin, int Win, int stride,
                                       const void* ifmap_nhwc, void* ofmap_nhwc, float alpha, void* stream);
 
+/* ---- Several GPUs driven from one process.  No counterpart in the reference project (it is
+ * single-GPU).  The path shards along the dense dimension with no exchange: every GPU holds a
+ * replica of the sparse operand and owns a contiguous slice of B's columns (SpMM) or of the
+ * batch (SpConv); its slice of the output is complete on its own.  Device ids are explicit;
+ * every call restores the caller's current device. */
+
+/* Even split of `total` units (dense columns with granule 8, images with granule 1) over `parts`
+ * shards in multiples of `granule`; the first shards get the larger sizes, trailing shards may be
+ * empty.  shard `index` owns [*begin, *begin + *count). */
+int shflbw_shard_range(long long total, int granule, int parts, int index, long long* begin, long long* count);
+
+/* Copy of a matrix / filter (host side only; the copy has no device image yet).  Replicate a
+ * sparse operand by hand: clone, cudaSetDevice, shflbw_matrix_to_device. */
+int shflbw_matrix_clone(const shflbw_matrix_t* m, shflbw_matrix_t** out);
+
+typedef struct shflbw_multi shflbw_multi_t;
+/* Uploads a replica of `m` to each of the n devices (ids may repeat) and makes one stream per shard. */
+int shflbw_multi_create(const shflbw_matrix_t* m, const int* device_ids, int n, shflbw_multi_t** out);
+void shflbw_multi_destroy(shflbw_multi_t* mg);
+int shflbw_multi_shards(const shflbw_multi_t* mg);
+/* Shard g computes D[g] (M x n_per_shard[g]) = alpha * A . B[g] (K x n_per_shard[g]); B[g] and D[g]
+ * are contiguous row-major buffers on device_ids[g].  n_per_shard[g] == 0 skips the shard. */
+int shflbw_multi_spmm_init(shflbw_multi_t* mg, const int* n_per_shard, const void* const* B, void* const* D, float alpha);
+/* Shard g convolves images_per_shard[g] NHWC images ifmap[g] -> ofmap[g] on device_ids[g]. */
+int shflbw_multi_spconv_init(shflbw_multi_t* mg, const int* images_per_shard, int Hin, int Win, int stride,
+                             const void* const* ifmap_nhwc, void* const* ofmap_nhwc, float alpha);
+/* Launches every shard on its own stream, one after the other, without waiting for any GPU. */
+int shflbw_multi_exec(shflbw_multi_t* mg);
+/* Waits for every shard; *max_ms (optional) = the largest device time of the last exec over the
+ * shards; returns SHFLBW_ERR_DEVICE_TIMEOUT if a shard's status word is set. */
+int shflbw_multi_sync(shflbw_multi_t* mg, float* max_ms);
+
 /* Number of kernel launches one exec call issues (for launch accounting). */
 int shflbw_spmm_launches_per_exec(const shflbw_spmm_state_t* st);
 int shflbw_spconv_launches_per_exec(const shflbw_spconv_state_t* st);

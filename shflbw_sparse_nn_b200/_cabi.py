@@ -114,6 +114,16 @@ _PROTOS = {
                                            C.c_int, C.c_int, C.c_float, C.c_int, C.POINTER(SpconvState)]),
     "shflbw_chain_residual_map": (C.c_int, [_H, _H, C.c_void_p]),
     "shflbw_spconv_chain_set_residual": (C.c_int, [_H, C.POINTER(SpconvState), C.c_void_p, C.c_void_p]),
+    "shflbw_shard_range": (C.c_int, [C.c_longlong, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_longlong), C.POINTER(C.c_longlong)]),
+    "shflbw_matrix_clone": (C.c_int, [_H, C.POINTER(_H)]),
+    "shflbw_multi_create": (C.c_int, [_H, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_void_p)]),
+    "shflbw_multi_destroy": (None, [C.c_void_p]),
+    "shflbw_multi_shards": (C.c_int, [C.c_void_p]),
+    "shflbw_multi_spmm_init": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_float]),
+    "shflbw_multi_spconv_init": (C.c_int, [C.c_void_p, C.POINTER(C.c_int), C.c_int, C.c_int, C.c_int,
+                                           C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_float]),
+    "shflbw_multi_exec": (C.c_int, [C.c_void_p]),
+    "shflbw_multi_sync": (C.c_int, [C.c_void_p, C.POINTER(C.c_float)]),
     "shflbw_spconv_exec_static_scratch": (C.c_int, [_H, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
                                                     C.c_float, C.c_void_p]),
 }

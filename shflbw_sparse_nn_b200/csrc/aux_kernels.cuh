@@ -16,6 +16,10 @@
 
 namespace shflbw {
 
+// Programmatic dependent launch (see sm100_ptx.cuh): both are no-ops for plain launches.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // in[n][hi][wi][c] (NHWC)  ->  Xs[c][hp][wp][Bp], the channel-major, batch-innermost staging
 // buffer with a zero halo: hp = hi + ph in [0, Hp), wp = wi + pw in [0, Wp); images n >= Bn and
 // halo pixels are written as zero, so every filter tap of every output pixel reads a valid
@@ -29,6 +33,8 @@ __global__ void __launch_bounds__(256)
 relayout_nhwc_to_chwn(const __half* __restrict__ in, __half* __restrict__ Xs, int Bn, int Bp, int Hin, int Win,
                       int Hp, int Wp, int ph, int pw, int C) {
     __shared__ __align__(16) __half tile[kRelayoutC * kRelayoutSlots];
+    grid_dep_launch();                       // the consumer may set itself up while this kernel runs
+    grid_dep_wait();                         // the staging buffer may still be read by the previous call's kernels
     const int NT = Bp < 32 ? Bp : 32;        // images per tile (a multiple of 8)
     const int PT = kRelayoutSlots / NT;      // padded pixels per tile
     const int n_tiles = (Bp + NT - 1) / NT;
@@ -95,6 +101,8 @@ unpermute_filters(const __half* __restrict__ staged, __half* __restrict__ out, c
     const int G = unperm_threads_per_pos(F), P = kUnpermThreads / G;
     const int slot = threadIdx.x / G, t = threadIdx.x - slot * G;   // position slot, thread within it
     for (int f = threadIdx.x; f < F; f += kUnpermThreads) sperm[f] = (unsigned short)__ldg(perm + f);
+    grid_dep_launch();
+    grid_dep_wait();                         // the staged output is complete only when the panel kernel is
     __half* mine = vec + (size_t)slot * F;
     for (int q0 = blockIdx.x * P; q0 < num_pos; q0 += gridDim.x * P) {
         const int q = q0 + slot;
@@ -129,6 +137,8 @@ chain_export_nhwc(const __half* __restrict__ buf, __half* __restrict__ out, cons
                   int Bn, int Bp, int H, int W, int Hp, int Wp, int ph, int pw, int F) {
     extern __shared__ __align__(16) uint8_t export_smem[];
     __half* vec = (__half*)export_smem;                  // [8 images][F]
+    grid_dep_launch();
+    grid_dep_wait();                                     // the planes are complete only when their producer is
     const int groups = Bp / 8;
     const int pix = blockIdx.x / groups, n0 = (blockIdx.x % groups) * 8;
     const int h = pix / W, w = pix - h * W;

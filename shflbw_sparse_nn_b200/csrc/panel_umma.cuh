@@ -254,6 +254,12 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
     sm100::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t smem_base = sm100::smem_u32(smem);
+    // Programmatic dependent launch: everything above (barriers, TMEM, the item table -- read from
+    // the sparse operand, which no kernel writes) may overlap the tail of the previous kernel in
+    // the stream; the dense operand, the residual and the output are touched only below.  The
+    // next kernel may start its own prologue as soon as every block of this one got here.
+    sm100::grid_dependency_launch();
+    sm100::grid_dependency_wait();
     if (tid == 0) TRACE(3, 0, 0);
     if (tid == 0) CTRACE(1);
 

@@ -14,6 +14,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <utility>
 
 #include "aux_kernels.cuh"
 #include "panel_umma.cuh"
@@ -35,6 +36,25 @@ bool cuda_ok(cudaError_t e, const char* what) {
     return false;
 }
 #define CK(call) do { if (!cuda_ok((call), #call)) return SHFLBW_ERR_CUDA; } while (0)
+
+// Every kernel of this library is launched with the programmatic-stream-serialization attribute:
+// it may start while the previous kernel of the stream drains, sets itself up (barriers, TMEM,
+// item table), and only then waits for that kernel's completion (griddepcontrol.wait in the
+// kernels).  Stream order of all data accesses is unchanged.  SHFLBW_PDL=0 turns it off.
+bool use_pdl() {
+    static const bool on = [] { const char* e = getenv("SHFLBW_PDL"); return !(e && atoi(e) == 0); }();
+    return on;
+}
+template <typename... Params, typename... Args>
+cudaError_t launch(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = use_pdl() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 int ensure_buffer(void** buf, size_t* have, size_t need) {
     if (*have >= need && *buf) return SHFLBW_OK;
@@ -462,7 +482,7 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
         if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
 #endif
-        ch.fn<<<dim3(st->grid_x, st->grid_y), ch.threads, ch.smem, s>>>(p);
+        CK(launch(ch.fn, dim3(st->grid_x, st->grid_y), dim3(ch.threads), ch.smem, s, p));
     }
     CK(cudaGetLastError());
     return SHFLBW_OK;
@@ -567,7 +587,7 @@ static void launch_relayout(const __half* in, __half* staged, int B, int Bp, int
     const int NT = Bp < 32 ? Bp : 32, PT = shflbw::kRelayoutSlots / NT;
     const int n_tiles = (Bp + NT - 1) / NT;
     dim3 grid((unsigned)(((PP + PT - 1) / PT) * n_tiles), (unsigned)((C + shflbw::kRelayoutC - 1) / shflbw::kRelayoutC));
-    shflbw::relayout_nhwc_to_chwn<<<grid, 256, 0, s>>>(in, staged, B, Bp, Hin, Win, Hp, Wp, R / 2, S / 2, C);
+    (void)launch(shflbw::relayout_nhwc_to_chwn, grid, dim3(256), 0, s, in, staged, B, Bp, Hin, Win, Hp, Wp, R / 2, S / 2, C);
 }
 
 // Dynamic shared memory of unpermute_filters: 16-bit permutation + one F-vector of fp16 per position.
@@ -725,20 +745,20 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
     if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
 #endif
-    ch.fn<<<dim3(st->grid_x, st->grid_y), ch.threads, ch.smem, s>>>(p);
+    CK(launch(ch.fn, dim3(st->grid_x, st->grid_y), dim3(ch.threads), ch.smem, s, p));
     // 3. back to NHWC in logical channel order.
     if (planes) {
         const long long blocks = (long long)st->Ho * st->Wo * (st->Bp / 8);
-        shflbw::chain_export_nhwc<<<(unsigned)blocks, 256, (size_t)st->F * 16, s>>>(
-            (const __half*)st->staged_out, (__half*)st->ofmap, nullptr, st->B, st->Bp, st->Ho, st->Wo, st->Ho, st->Wo,
-            0, 0, st->F);
+        CK(launch(shflbw::chain_export_nhwc, dim3((unsigned)blocks), dim3(256), (size_t)st->F * 16, s,
+                  (const __half*)st->staged_out, (__half*)st->ofmap, (const int*)nullptr, st->B, st->Bp, st->Ho, st->Wo,
+                  st->Ho, st->Wo, 0, 0, st->F));
     } else if (st->staged_out) {
         const int num_pos = st->B * st->Ho * st->Wo;
         const int per_block = shflbw::kUnpermThreads / shflbw::unperm_threads_per_pos(st->F);
         int blocks = (num_pos + per_block - 1) / per_block;
         if (blocks > 148 * 16) blocks = 148 * 16;
-        shflbw::unpermute_filters<<<blocks, shflbw::kUnpermThreads, unperm_smem_bytes(st->F), s>>>(
-            (const __half*)st->staged_out, (__half*)st->ofmap, st->perm, num_pos, st->F);
+        CK(launch(shflbw::unpermute_filters, dim3(blocks), dim3(shflbw::kUnpermThreads), unperm_smem_bytes(st->F), s,
+                  (const __half*)st->staged_out, (__half*)st->ofmap, st->perm, num_pos, st->F));
     }
     CK(cudaGetLastError());
     return SHFLBW_OK;
@@ -830,8 +850,8 @@ int shflbw_chain_export_nhwc(const void* chain_buf, int B, int H, int W, int F, 
     const int Bp = (B + 7) / 8 * 8;
     const long long blocks = (long long)H * W * (Bp / 8);
     if (blocks >= (1ll << 31)) return SHFLBW_ERR_UNSUPPORTED;
-    shflbw::chain_export_nhwc<<<(unsigned)blocks, 256, smem, (cudaStream_t)stream>>>(
-        (const __half*)chain_buf, (__half*)nhwc, perm, B, Bp, H, W, H + R - 1, W + S - 1, R / 2, S / 2, F);
+    CK(launch(shflbw::chain_export_nhwc, dim3((unsigned)blocks), dim3(256), smem, (cudaStream_t)stream,
+              (const __half*)chain_buf, (__half*)nhwc, perm, B, Bp, H, W, H + R - 1, W + S - 1, R / 2, S / 2, F));
     CK(cudaGetLastError());
     return SHFLBW_OK;
 }
@@ -947,6 +967,135 @@ int shflbw_spconv_exec_static_scratch(const shflbw_matrix_t* f, int B, int Hin, 
     if (st.staged_out_bytes) st.staged_out = scratch + in_bytes;
     st.init_success = 1;
     return shflbw_spconv_exec(&st, stream);
+}
+
+// ---- several GPUs from one process -------------------------------------------------------
+
+struct shflbw_multi {
+    struct Shard {
+        int device = -1;
+        shflbw_matrix_t* mat = nullptr;      // replica of the sparse operand on `device`
+        cudaStream_t stream = nullptr;
+        cudaEvent_t start = nullptr, stop = nullptr;
+        int kind = 0;                        // 0 none, 1 SpMM, 2 SpConv
+        shflbw_spmm_state_t spmm;
+        shflbw_spconv_state_t conv;
+    };
+    std::vector<Shard> shards;
+};
+
+namespace {
+struct DeviceGuard {                         // restores the caller's current device
+    int prev = -1;
+    DeviceGuard() { cudaGetDevice(&prev); }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+}  // namespace
+
+int shflbw_multi_create(const shflbw_matrix_t* m, const int* device_ids, int n, shflbw_multi_t** out) {
+    if (!m || !device_ids || n <= 0 || n > kMaxDevices || !out) return SHFLBW_ERR_INVALID_ARG;
+    *out = nullptr;
+    int have = 0;
+    CK(cudaGetDeviceCount(&have));
+    for (int g = 0; g < n; ++g) if (device_ids[g] < 0 || device_ids[g] >= have) return SHFLBW_ERR_INVALID_ARG;
+    DeviceGuard guard;
+    auto* mg = new shflbw_multi;
+    mg->shards.resize(n);
+    int rc = SHFLBW_OK;
+    for (int g = 0; g < n && rc == SHFLBW_OK; ++g) {
+        auto& sh = mg->shards[g];
+        sh.device = device_ids[g];
+        if (!cuda_ok(cudaSetDevice(sh.device), "cudaSetDevice")) { rc = SHFLBW_ERR_CUDA; break; }
+        if ((rc = shflbw_matrix_clone(m, &sh.mat)) != SHFLBW_OK) break;
+        if ((rc = shflbw_matrix_to_device(sh.mat)) != SHFLBW_OK) break;
+        if (!cuda_ok(cudaStreamCreateWithFlags(&sh.stream, cudaStreamNonBlocking), "cudaStreamCreate") ||
+            !cuda_ok(cudaEventCreate(&sh.start), "cudaEventCreate") || !cuda_ok(cudaEventCreate(&sh.stop), "cudaEventCreate"))
+            rc = SHFLBW_ERR_CUDA;
+    }
+    if (rc != SHFLBW_OK) { shflbw_multi_destroy(mg); return rc; }
+    *out = mg;
+    return SHFLBW_OK;
+}
+
+void shflbw_multi_destroy(shflbw_multi_t* mg) {
+    if (!mg) return;
+    DeviceGuard guard;
+    for (auto& sh : mg->shards) {
+        if (sh.device >= 0) cudaSetDevice(sh.device);
+        if (sh.stream) { cudaStreamSynchronize(sh.stream); cudaStreamDestroy(sh.stream); }
+        if (sh.start) cudaEventDestroy(sh.start);
+        if (sh.stop) cudaEventDestroy(sh.stop);
+        shflbw_matrix_destroy(sh.mat);
+    }
+    delete mg;
+}
+
+int shflbw_multi_shards(const shflbw_multi_t* mg) { return mg ? (int)mg->shards.size() : 0; }
+
+int shflbw_multi_spmm_init(shflbw_multi_t* mg, const int* n_per_shard, const void* const* B, void* const* D, float alpha) {
+    if (!mg || !n_per_shard || !B || !D) return SHFLBW_ERR_INVALID_ARG;
+    DeviceGuard guard;
+    for (size_t g = 0; g < mg->shards.size(); ++g) {
+        auto& sh = mg->shards[g];
+        sh.kind = 0;
+        if (n_per_shard[g] == 0) continue;                    // an empty shard is legal: nothing to launch
+        CK(cudaSetDevice(sh.device));
+        const int rc = shflbw_spmm_init(sh.mat, n_per_shard[g], B[g], alpha, nullptr, 0.f, D[g], SHFLBW_KERNEL_AUTO, &sh.spmm);
+        if (rc != SHFLBW_OK) return rc;
+        sh.kind = 1;
+    }
+    return SHFLBW_OK;
+}
+
+int shflbw_multi_spconv_init(shflbw_multi_t* mg, const int* images_per_shard, int Hin, int Win, int stride,
+                             const void* const* ifmap, void* const* ofmap, float alpha) {
+    if (!mg || !images_per_shard || !ifmap || !ofmap) return SHFLBW_ERR_INVALID_ARG;
+    DeviceGuard guard;
+    for (size_t g = 0; g < mg->shards.size(); ++g) {
+        auto& sh = mg->shards[g];
+        sh.kind = 0;
+        if (images_per_shard[g] == 0) continue;
+        CK(cudaSetDevice(sh.device));
+        const int rc = shflbw_spconv_init(sh.mat, images_per_shard[g], Hin, Win, stride, ifmap[g], ofmap[g], alpha,
+                                          SHFLBW_KERNEL_AUTO, &sh.conv);
+        if (rc != SHFLBW_OK) return rc;
+        sh.kind = 2;
+    }
+    return SHFLBW_OK;
+}
+
+int shflbw_multi_exec(shflbw_multi_t* mg) {
+    if (!mg) return SHFLBW_ERR_INVALID_ARG;
+    DeviceGuard guard;
+    for (auto& sh : mg->shards) {                              // back to back: nothing here waits for a GPU
+        if (!sh.kind) continue;
+        CK(cudaSetDevice(sh.device));
+        CK(cudaEventRecord(sh.start, sh.stream));
+        const int rc = sh.kind == 1 ? shflbw_spmm_exec(&sh.spmm, sh.stream) : shflbw_spconv_exec(&sh.conv, sh.stream);
+        if (rc != SHFLBW_OK) return rc;
+        CK(cudaEventRecord(sh.stop, sh.stream));
+    }
+    return SHFLBW_OK;
+}
+
+int shflbw_multi_sync(shflbw_multi_t* mg, float* max_ms) {
+    if (!mg) return SHFLBW_ERR_INVALID_ARG;
+    DeviceGuard guard;
+    float worst = 0.f;
+    int status = SHFLBW_OK;
+    for (auto& sh : mg->shards) {
+        CK(cudaSetDevice(sh.device));
+        CK(cudaStreamSynchronize(sh.stream));
+        if (sh.kind) {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, sh.start, sh.stop) == cudaSuccess && ms > worst) worst = ms;
+            else (void)cudaGetLastError();
+            const int rc = shflbw_matrix_device_status(sh.mat);
+            if (rc != SHFLBW_OK) status = rc;
+        }
+    }
+    if (max_ms) *max_ms = worst;
+    return status;
 }
 
 }  // extern "C"

@@ -418,6 +418,33 @@ int shflbw_matrix_dump_file(const shflbw_matrix_t* m, const char* path) {
 
 int shflbw_matrix_validate(const shflbw_matrix_t* m) { return m ? validate(*m) : SHFLBW_ERR_INVALID_ARG; }
 
+int shflbw_matrix_clone(const shflbw_matrix_t* m, shflbw_matrix_t** out) {
+    if (!m || !out) return SHFLBW_ERR_INVALID_ARG;
+    auto* c = new shflbw_matrix(*m);
+    // the copy owns nothing on any device
+    c->device = -1;
+    c->d_meta = c->d_val = nullptr;
+    c->d_kptr = c->d_kidx = c->d_kcrs = c->d_perm = nullptr;
+    c->d_status = nullptr;
+    c->stage_in = c->stage_c = c->stage_out = c->conv_in = c->conv_out = nullptr;
+    c->stage_in_bytes = c->stage_c_bytes = c->stage_out_bytes = c->conv_in_bytes = c->conv_out_bytes = 0;
+    c->retired.clear();
+    for (void*& st : c->host_streams) st = nullptr;
+    for (void*& ev : c->host_events) ev = nullptr;
+    *out = c;
+    return SHFLBW_OK;
+}
+
+int shflbw_shard_range(long long total, int granule, int parts, int index, long long* begin, long long* count) {
+    if (total < 0 || granule <= 0 || parts <= 0 || index < 0 || index >= parts || !begin || !count)
+        return SHFLBW_ERR_INVALID_ARG;
+    if (total % granule) return SHFLBW_ERR_UNSUPPORTED;
+    const long long groups = total / granule, base = groups / parts, extra = groups % parts;
+    *begin = ((long long)index * base + (index < extra ? index : extra)) * granule;
+    *count = (base + (index < extra ? 1 : 0)) * granule;
+    return SHFLBW_OK;
+}
+
 void shflbw_matrix_destroy(shflbw_matrix_t* m) {
     if (!m) return;
     drop_device_copy(*m);

@@ -137,6 +137,16 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+// ------------------------------------------- programmatic dependent launch ----
+// A kernel launched with the programmatic-stream-serialization attribute may start while the
+// kernel before it in the stream is still running.  grid_dependency_wait() blocks until that
+// kernel has completed and its writes are visible (no-op without the attribute);
+// grid_dependency_launch() lets the NEXT kernel of the stream start early (no-op when that one
+// was launched without the attribute).  Everything a kernel does before its wait must not touch
+// data the previous kernel writes -- or buffers it still reads.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------- register budgets ----
 // Change the per-thread register budget of the executing warpgroup (4 consecutive warps, all
 // of which must execute the same instruction).  The count is a multiple of 8 in [24, 256].

@@ -20,8 +20,8 @@ exchange) and the per-layer time is the maximum over the ranks.
 
 Timing follows the reference's tool (benchmark/benchmark.spmm.cu:36-49): warm-up launches,
 then the mean over `reps` launches between two CUDA events.  Inputs alternate between buffers
-whose total size exceeds the L2 cache.  Peaks come from --hbm-gbs / --tflops (defaults: the
-copy bandwidth and fp16 tensor throughput measured on the B200 this was developed on)."""
+whose total size exceeds the L2 cache.  Peaks come from --hbm-gbs / --tflops (defaults: a measured
+copy bandwidth and dense fp16 tensor throughput of one B200)."""
 from __future__ import annotations
 
 import argparse

@@ -31,18 +31,18 @@ from shflbw_sparse_nn_b200.blockwise import uniform_half  # noqa: E402
 
 import os  # noqa: E402
 
-# checkout of the reference project (same default as oracle/Makefile's REF)
-REF_GOLDEN = Path(os.environ.get("REF", "/root/reference")) / "example" / "mtx_dump.txt"
+# checkout of the reference project (same default as oracle/Makefile's REF: a sibling of this repository)
+REF_GOLDEN = Path(os.environ.get("REF", str(HERE.parent.parent.parent / "reference"))) / "example" / "mtx_dump.txt"
 
 BUILDER_GRID = [
     # nrow, ncol, brow, density, permute, seed
-    (256, 256, 32, 0.1, True, 2021),     # BASELINE config 1
+    (256, 256, 32, 0.1, True, 2021),     # small correctness case (V=32)
     (1024, 1024, 32, 0.2, False, 2021),  # the reference's example / golden dump
     (1024, 1024, 16, 0.1, True, 2021),   # reference test shape, V=16
     (1024, 1024, 64, 0.1, True, 2021),
     (1024, 1024, 128, 0.1, False, 2021),
-    (4096, 4096, 64, 0.1, True, 2021),   # BASELINE config 2 (headline)
-    (2048, 4608, 64, 0.1, True, 2021),   # BASELINE config 3 filter matrix
+    (4096, 4096, 64, 0.1, True, 2021),   # headline SpMM shape
+    (2048, 4608, 64, 0.1, True, 2021),   # headline SpConv filter matrix (2048 x 3*3*512)
     (768, 3072, 128, 0.05, True, 7),
     (64, 64, 64, 0.2, True, 3),          # single row block, K smaller than one stage
     (128, 96, 32, 0.5, False, 11),

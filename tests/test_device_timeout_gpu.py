@@ -9,8 +9,8 @@ The failure is made on purpose in a separate build of the library (-DSHFLBW_FAUL
 product library has no such switch): one producer warp stops arriving on the "stage is full"
 barriers, so the MMA thread's wait for that stage can never complete.  With the limit lowered to
 about a millisecond the launch must come back quickly, `shflbw_matrix_device_status` must report
-SHFLBW_ERR_DEVICE_TIMEOUT with the "full stage" code, and the next ordinary launch must give
-the correct result again.
+SHFLBW_ERR_DEVICE_TIMEOUT with the code of a waiter downstream of the withheld stage, and the
+next ordinary launch must give the correct result again.
 """
 import ctypes as C
 import time
@@ -62,7 +62,9 @@ def test_wait_limit_runs_out_and_the_library_recovers(swap, monkeypatch):
         launch()                                              # returns: the wait gave up
         assert time.perf_counter() - t0 < 2.0
         assert flib.shflbw_matrix_device_status(h) == _cabi.ERR_DEVICE_TIMEOUT
-        assert "status word = 1" in flib.shflbw_last_cuda_error().decode()     # SHFLBW_DEVSTAT_TIMEOUT_FULL
+        # whichever waiter's limit passes first records its code: the MMA thread waiting for the
+        # stage (1, TIMEOUT_FULL) or an epilogue warp waiting for the accumulator behind it (3)
+        assert flib.shflbw_last_cuda_error().decode() in ("device status word = 1", "device status word = 3")
         assert flib.shflbw_matrix_device_status(h) == _cabi.OK                 # reading the word clears it
 
         # back to normal: same launch, correct result, clean status

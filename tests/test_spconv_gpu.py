@@ -81,7 +81,7 @@ def test_simt_cross_check_kernel_matches_oracle():
 
 
 def test_headline_16x14x14x512_to_2048():
-    """BASELINE config 3 at full size."""
+    """The headline SpConv (16x14x14x512 -> 2048, 3x3, V=64, d=0.1, permuted) at full size."""
     Bn, H, W, Cc, F, V = 16, 14, 14, 512, 2048, 64
     f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, V, 1, 0.1, True, 2021, values="uniform")
     assert f.nnzb == 14746
@@ -96,14 +96,22 @@ def test_headline_16x14x14x512_to_2048():
     assert_close_fp16(O, _oracle(f, Bn, H, W, 1, x), what="config 3 vs oracle")
     O_simt, _ = run_spconv(f, Bn, H, W, 1, x, kernel=sb.KERNEL_SIMT)
     assert_close_fp16(O, O_simt.astype(np.float32), what="config 3 vs simt")
-    if oa.ref_gpu() is not None:
-        # reference kernel: input [C][H][W][B], output [F][H][W][B]
-        xd = dev(np.ascontiguousarray(x.transpose(3, 1, 2, 0)))
-        od = torch.zeros((F, H, W, Bn), dtype=torch.float16, device="cuda")
-        cfg = oa.ref_gpu_conv_configs(V)[0][0]
-        rc, _ = oa.ref_gpu_spconv(cfg, Bn, H, W, Cc, F, 3, 3, 1, V, indptr, indices, values, perm, xd.data_ptr(), od.data_ptr())
-        assert rc == 0
-        assert_close_fp16(O, host(od).astype(np.float32).transpose(3, 1, 2, 0), what="config 3 vs reference CUDA kernel")
+
+
+@pytest.mark.skipif(oa.ref_gpu() is None, reason="oracle/_ref/libshflbw_ref_gpu.so (the reference's CUDA kernels) is not built")
+def test_headline_against_the_reference_cuda_kernel():
+    """Same shape against the reference's own kernel (its layouts: input [C][H][W][B], output [F][H][W][B])."""
+    Bn, H, W, Cc, F, V = 16, 14, 14, 512, 2048, 64
+    f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, V, 1, 0.1, True, 2021, values="uniform")
+    x = sb.uniform_half(8, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    O, _ = run_spconv(f, Bn, H, W, 1, x)
+    indptr, indices, values, perm = _arrays(f)
+    xd = dev(np.ascontiguousarray(x.transpose(3, 1, 2, 0)))
+    od = torch.zeros((F, H, W, Bn), dtype=torch.float16, device="cuda")
+    cfg = oa.ref_gpu_conv_configs(V)[0][0]
+    rc, _ = oa.ref_gpu_spconv(cfg, Bn, H, W, Cc, F, 3, 3, 1, V, indptr, indices, values, perm, xd.data_ptr(), od.data_ptr())
+    assert rc == 0
+    assert_close_fp16(O, host(od).astype(np.float32).transpose(3, 1, 2, 0), what="config 3 vs reference CUDA kernel")
 
 
 def test_host_buffer_call_equals_device_call():

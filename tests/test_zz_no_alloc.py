@@ -65,7 +65,8 @@ def test_static_scratch_matches_regular_path_twice(permute):
     assert_close_fp16(got2, ref2.astype(np.float32), what="static scratch, call 2")
     assert np.array_equal(got1.view(np.uint16), ref1.view(np.uint16))
     assert np.array_equal(got2.view(np.uint16), ref2.view(np.uint16))
-    want = 0.5 * oa.spconv_ref_nhwc(Bn, H, W, Cc, F, 3, 3, 1, V, f.indptr, f.indices, f.values, f.row_permute_ids, x1)
+    want = 0.5 * oa.spconv_ref_nhwc(Bn, H, W, Cc, F, 3, 3, 1, V, f.indptr, f.indices, f.values,
+                                    f.row_permute_ids if permute else None, x1)
     assert_close_fp16(got1, want, what="static scratch vs CPU oracle")
 
 
