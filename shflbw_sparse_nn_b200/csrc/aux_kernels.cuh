@@ -159,6 +159,42 @@ chain_export_nhwc(const __half* __restrict__ buf, __half* __restrict__ out, cons
     }
 }
 
+// planes[f][tok] -> out[n][pix][f]: the output of an NHWC call computed as planes (one row of
+// tok = pix * Bp + n tokens per LOGICAL filter f) transposed to NHWC.  One block moves a tile of
+// 64 filters x 64 tokens through 8 KB of shared memory: 16-byte loads of 8 tokens of one
+// filter, 2-byte scatters into [token][filter] (8-filter groups XOR-swizzled by the token group,
+// so neither side has bank conflicts), 16-byte stores of 8 filters of one token -- 128-byte runs
+// in global memory on both sides.  F % 64 == 0, Bp % 8 == 0; images n >= Bn are padding.
+__global__ void __launch_bounds__(256)
+planes_to_nhwc(const __half* __restrict__ planes, __half* __restrict__ out, int Bn, int Bp, int npix, int F) {
+    __shared__ __align__(16) __half tile[64 * 64];
+    grid_dep_launch();
+    grid_dep_wait();                                     // the planes are complete only when the panel kernel is
+    const int ntok = npix * Bp;
+    const int tok0 = blockIdx.x * 64, f0 = blockIdx.y * 64;
+    const int c = threadIdx.x & 7, r0 = threadIdx.x >> 3;   // 16-byte chunk, row of the pass
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const int r = r0 + 32 * pass;                    // filter of the tile
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (tok0 + c * 8 < ntok) v = *(const uint4*)(planes + (size_t)(f0 + r) * ntok + tok0 + c * 8);
+        const __half* h = (const __half*)&v;
+        const int col = (((r >> 3) ^ c) << 3) | (r & 7);    // token group c: filter group XOR c
+#pragma unroll
+        for (int j = 0; j < 8; ++j) tile[(c * 8 + j) * 64 + col] = h[j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+        const int t = r0 + 32 * pass;                    // token of the tile
+        const int tok = tok0 + t;
+        const int pix = tok / Bp, n = tok - pix * Bp;
+        if (tok < ntok && n < Bn)
+            *(uint4*)(out + ((size_t)n * npix + pix) * F + f0 + c * 8) =
+                *(const uint4*)(tile + t * 64 + ((c ^ ((t >> 3) & 7)) << 3));
+    }
+}
+
 // Plain SpMM: one thread per (stored row, dense column); grid = (rows, column tiles).
 __global__ void simt_spmm(const int* __restrict__ blk_ptr, const int* __restrict__ blk_idx,
                           const __half* __restrict__ blk_val, const int* __restrict__ perm,

@@ -88,6 +88,7 @@ struct alignas(64) PanelParams {
     int Bn, Bp, Hp, Wp, Cin, F, R, S, stride, Ho, Wo;
     // chained SpConv: out[f][OHp][OWp][Bp] with the next layer's halo (origin at (oph, opw))
     int OWp, oph, opw, out_plane, relu;
+    int wide_stores;         // SpMM, rows in lanes: output rows are 32-byte aligned (N % 16 == 0, D % 32 == 0)
     int out_logical;         // chained kernels: output plane of stored filter f is perm[f] (logical channel order) instead of f
     const __half* res;       // optional residual in the OUTPUT's geometry ([planes][OHp][OWp][Bp]) or nullptr
     const int* res_map;      // stored filter -> plane of `res` (nullptr: same index)
@@ -141,13 +142,16 @@ struct PanelCfg {
     static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
     // Each epilogue warp transposes 32 tokens x 32 output rows / filters through 2 KB so that
     // its global stores are 16 bytes per lane and 64-byte runs.
-    static constexpr int OUT_BYTES = 8 * 2048;
+    // Epilogue tiles (tokens in lanes only): each epilogue warp transposes 32 tokens x 32 output
+    // rows / filters through 2 KB so that its global stores are 16 bytes per lane and 64-byte
+    // runs.  With rows in lanes the stores go straight from registers.
+    static constexpr int OUT_BYTES = (MODE == kPanelSpmmRows || MODE == kPanelConvChainRows) ? 0 : 8 * 2048;
     static constexpr int BAR_BYTES = (STAGES * 2 + 8) * 8;   // mbarriers + tmem slot + abort flag
     static constexpr int TAB_BYTES = 512 * 8;               // per-CTA item table (kPanelMaxItemsPerCta entries)
     static constexpr int IDX_AHEAD = LAG + 1;              // a group fetches row ids this many of its stages ahead
     static constexpr int IDX_RING = (IDX_AHEAD + 1) * GROUPS <= 8 ? 8 : 16;   // stages of row ids kept in shared memory
     static_assert((IDX_AHEAD + 1) * GROUPS <= IDX_RING, "row-id ring too small");
-    static constexpr int IDX_BYTES = IDX_RING * KS * 4;
+    static constexpr int IDX_BYTES = TMA ? 0 : IDX_RING * KS * 4;   // (the TMA gather loads its row ids straight into registers)
     static constexpr int SMEM_BYTES = PIPE_BYTES + OUT_BYTES + BAR_BYTES + TAB_BYTES + IDX_BYTES + 1024;  // + align slack
     static constexpr bool SWAP = MODE == kPanelSpmmRows || MODE == kPanelConvChainRows;
     static constexpr int KG_BYTES = SWAP ? T * 16 : 2048;   // 8 gathered rows (one K group) of the token tile
@@ -156,12 +160,12 @@ struct PanelCfg {
     static constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // double buffered
     static_assert(V == 16 || V == 32 || V == 64 || V == 128, "row-block height");
     static_assert(V != 16 || (TM == 1 && !SWAP), "16-row blocks: tokens in lanes, one 128-token accumulator");
-    static_assert(!TMA || MODE == kPanelSpmmRows, "TMA gather: SpMM with rows in lanes");
+    static_assert(!TMA || (MODE == kPanelSpmmRows && V == 64), "TMA gather: SpMM with rows in lanes, 64-row blocks");
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte swizzle-atom alignment");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
     static_assert(KS % 16 == 0 && PW % GROUPS == 0 && KS % (PW / GROUPS) == 0 && (KS / (PW / GROUPS)) % (32 / (T / 8)) == 0,
                   "rows per producer warp");
-    static_assert(LAG >= 1 && LAG <= 2 && STAGES > GROUPS * LAG, "publish lag");
+    static_assert(LAG >= 1 && LAG <= 2 && (TMA || STAGES > GROUPS * LAG), "publish lag");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -301,7 +305,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             c.num_k = 0; c.row_begin = 0; c.rows_total = 0;
         };
         auto advance = [&](Cursor& c) { if (++c.kt >= c.num_k) { ++c.li; enter(c); } };
-        // The 4 row ids of this lane's quad, loaded one of the group's stages ahead (registers).
+        // The 4 row ids of this lane's quad, loaded two of the group's stages ahead (registers).
         auto load_ids = [&](const Cursor& c) {
             const int r = c.kt * KS + quad * 4;
             if (issuer && c.li < nloc && r < c.rows_total) return __ldg((const int4*)(p.blk_idx + c.row_begin + r));
@@ -310,9 +314,14 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         Cursor pre{0, 0, 0, 0, 0};
         enter(pre);
         for (int d = 0; d < grp; ++d) advance(pre);
-        int4 ids = load_ids(pre);
+        int4 ids = load_ids(pre);                            // this group's first stage
         for (int g = 0; g < GROUPS; ++g) advance(pre);
+        int4 ids_next = load_ids(pre);                       // and its second: two stages of ids are in flight,
+        for (int g = 0; g < GROUPS; ++g) advance(pre);       // which covers the load's latency even with one group
         int it = 0;
+#ifdef SHFLBW_COUNTERS
+        long long pc_empty = 0, pc_n = 0, pc_t0 = clock64();
+#endif
         for (int li = 0; li < nloc; ++li) {
             const int2 ent = item_tab[li];
             const int num_k = (ent.y + KS - 1) / KS;
@@ -324,11 +333,17 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                 if ((it % GROUPS) != grp) continue;
                 const int s = it % STAGES;
                 if (it >= STAGES) {
+#ifdef SHFLBW_COUNTERS
+                    const long long e0c = clock64();
+#endif
                     int ok = 1;
                     if (lane == 0)
                         ok = sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
                                                       SHFLBW_DEVSTAT_TIMEOUT_EMPTY, p.wait_limit, 32);
                     if (!__shfl_sync(0xffffffffu, ok, 0)) goto tma_producer_done;
+#ifdef SHFLBW_COUNTERS
+                    pc_empty += clock64() - e0c; ++pc_n;
+#endif
                 }
                 const int rows_valid = min(KS, ent.y - kt * KS);    // multiple of 16
                 const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
@@ -345,11 +360,18 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                     if (!(ablate & 2)) sm100::tma_gather4(st_base + dst_off, p.tmap_b, col, ids.x, ids.y, ids.z, ids.w, &full_bar[s]);
                     else sm100::mbar_complete_tx(&full_bar[s], 512u);
                 }
-                ids = load_ids(pre);
+                ids = ids_next;
+                ids_next = load_ids(pre);
                 for (int g = 0; g < GROUPS; ++g) advance(pre);
             }
         }
     tma_producer_done:;
+#ifdef SHFLBW_COUNTERS
+        if (lane == 0 && p.trace != nullptr && pidx < 8) {
+            unsigned long long* o = p.trace + 148 * 16 + (blockIdx.x * 8 + pidx) * 4;
+            o[0] = pc_empty; o[1] = pc_n; o[2] = clock64() - pc_t0;
+        }
+#endif
         }
     } else if (warp >= 9) {
         // ------------------------------------------------------------- producers ----
@@ -615,13 +637,26 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                         goto mma_done;                       // timed out or aborted: issue nothing more
 #endif
                     TRACE(1, it, 0);
-                    if (!(ablate & 16)) sm100::fence_proxy_async_smem();  // cp.async (generic proxy) data -> tensor-core (async proxy) reads
+                    // cp.async (generic proxy) data -> tensor-core (async proxy) reads; the copy engine's
+                    // writes of the TMA gather are in the async proxy already
+                    if (!Cfg::TMA && !(ablate & 16)) sm100::fence_proxy_async_smem();
                     sm100::tc_fence_after_sync();
-                    const int nk = (ablate & 1) ? 0 : min(KS, rows_total - kt * KS) / 16;
-                    // compact loop (not unrolled): the three roles share a small instruction cache
+                    int nk = (ablate & 1) ? 0 : min(KS, rows_total - kt * KS) / 16;
                     uint64_t gdj = gdesc0 + (uint64_t)((s * (uint32_t)Cfg::STAGE_BYTES) >> 4);
                     uint64_t wdj = wdesc0 + (uint64_t)((s * (uint32_t)Cfg::STAGE_BYTES) >> 4);
                     uint32_t accum = (uint32_t)(kt != 0);
+                    if constexpr (SWAP) {
+                        // A full stage (the common case) is issued as straight-line code: one thread
+                        // issues every MMA, so the scalar work between two of them is what limits
+                        // the issue rate; the descriptor steps are immediates here.
+                        if (nk == KS / 16) {
+#pragma unroll
+                            for (int j = 0; j < KS / 16; ++j)
+                                sm100::umma_f16_ss(acc_base, wdj + (uint64_t)(j * (WSTEP >> 4)), gdj + (uint64_t)(j * ((2 * Cfg::KG_BYTES) >> 4)),
+                                                   idesc, j == 0 ? accum : 1u);
+                            nk = 0;
+                        }
+                    }
 #pragma unroll 1
                     for (int j = 0; j < nk; ++j) {
                         if constexpr (SWAP) {
@@ -681,7 +716,13 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         const bool reads = half_id < HALVES;
         const __half alpha1 = __float2half_rn(p.alpha), beta1 = __float2half_rn(p.beta);
         const __half2 alpha2 = __half2half2(alpha1);
+#ifdef SHFLBW_COUNTERS
+        long long ec_wait = 0, ec_t0 = clock64();
+#endif
         for (int li = 0; li < nloc; ++li) {
+#ifdef SHFLBW_COUNTERS
+            const long long ew0 = clock64();
+#endif
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
             const int blk = item / p.tiles_n;
             const int n0 = (item % p.tiles_n) * T;
@@ -693,41 +734,38 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                                                   SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 32);
             if (!__shfl_sync(0xffffffffu, acc_ok, 0)) break;    // timed out or aborted: store nothing more
             sm100::tc_fence_after_sync();
+#ifdef SHFLBW_COUNTERS
+            ec_wait += clock64() - ew0;
+#endif
             if (tid == 0) TRACE(2, li, 0);
             if constexpr (SWAP) {
                 // Rows in lanes: lane l of quadrant `quad` holds output row m of the block (V = 64:
                 // the quadrant's first 16 lanes, m = 16*quad + l; V = 128: all 32, m = 32*quad + l)
                 // and this warp reads token columns [half_id*T/2, +T/2), 32 at a time: a lane's 32
-                // tokens are 64 contiguous bytes of its D row.  They are packed to fp16, staged
-                // row by row in a swizzled shared-memory tile and stored 16 bytes per lane with
-                // four lanes per row, so that a store instruction touches 8 rows x 64 bytes.
+                // tokens are 64 contiguous bytes of its output row.  They are packed to fp16 and
+                // stored straight from registers -- as two 32-byte stores (whole L2 sectors) when
+                // the output rows are 32-byte aligned, else as four 16-byte stores.  No shared
+                // memory is involved: the tensor core's operand reads and the gather's writes already
+                // use most of its bandwidth.
                 constexpr int LR = V == 64 ? 16 : 32;                    // rows (valid lanes) per quadrant
                 constexpr int HC = T / 2;                                // token columns of this warp
-                uint8_t* tile = smem + Cfg::PIPE_BYTES + warp * 2048;    // [LR rows][64 bytes]
                 const uint32_t acc0 = tmem_base + ((uint32_t)(quad * 32) << 16) + b * Cfg::ACC_COLS + half_id * HC;
                 const int m = quad * LR + (lane < LR ? lane : 0);
-                uint32_t my_roff;                                        // element offset of this lane's output row
+                size_t roff;                                             // element offset of this lane's output row
+                size_t rres = 0;                                         // chained: offset of its residual row
+                const bool use_res = CHAIN && p.res != nullptr;
                 if constexpr (CHAIN) {
                     // plane of this filter: stored order between chained layers, logical order when the
                     // planes are about to be transposed to NHWC
                     const int plane = (p.out_logical && p.perm) ? __ldg(p.perm + blk * V + m) : blk * V + m;
-                    my_roff = (uint32_t)plane * (uint32_t)p.out_plane;
+                    roff = (size_t)plane * (size_t)p.out_plane;
+                    if (use_res) rres = (size_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (size_t)p.out_plane;
                 } else {
                     const int drow = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
-                    my_roff = (uint32_t)drow * (uint32_t)p.N;
+                    roff = (size_t)drow * (size_t)p.N;
                 }
                 __half* const obase = CHAIN ? p.out : p.D;
                 const __half2 zero2 = __float2half2_rn(0.f);
-                uint32_t roff[LR / 8];                                   // D offsets of rows 8i + lane/4
-#pragma unroll
-                for (int i = 0; i < LR / 8; ++i) roff[i] = __shfl_sync(0xffffffffu, my_roff, i * 8 + (lane >> 2));
-                uint32_t rres[LR / 8];                                   // chained: residual offsets of those rows
-                const bool use_res = CHAIN && p.res != nullptr;
-                if (use_res) {
-                    const uint32_t mine = (uint32_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (uint32_t)p.out_plane;
-#pragma unroll
-                    for (int i = 0; i < LR / 8; ++i) rres[i] = __shfl_sync(0xffffffffu, mine, i * 8 + (lane >> 2));
-                }
                 const bool use_c = !CHAIN && p.beta != 0.0f && p.C != nullptr;
 #pragma unroll 1
                 for (int cc = 0; cc < HC; cc += 32) {
@@ -745,49 +783,52 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                         if (lane == 0) sm100::mbar_arrive(&acc_empty[b]);
                         if (tid == 0) TRACE(2, li, 1);
                     }
-                    if (lane < LR) {
+                    if (lane < LR && !(ablate & 520)) {
+                    const int tok0 = n0 + half_id * HC + cc;             // this lane's 32 tokens start here
+                    uint4 v[4];
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            uint4 v;
-                            __half2* h = (__half2*)&v;
+                    for (int c = 0; c < 4; ++c) {
+                        __half2* h = (__half2*)&v[c];
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                // same arithmetic as the reference: round to fp16, then alpha in fp16
-                                h[e] = __floats2half2_rn(__uint_as_float(r[c * 8 + 2 * e]), __uint_as_float(r[c * 8 + 2 * e + 1]));
-                                if (!use_c) h[e] = __hmul2(h[e], alpha2);
-                            }
-                            *(uint4*)(tile + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) = v;
+                        for (int e = 0; e < 4; ++e) {
+                            // same arithmetic as the reference: round to fp16, then alpha in fp16
+                            h[e] = __floats2half2_rn(__uint_as_float(r[c * 8 + 2 * e]), __uint_as_float(r[c * 8 + 2 * e + 1]));
+                            if (!use_c) h[e] = __hmul2(h[e], alpha2);
                         }
                     }
-                    __syncwarp();
-                    if (!(ablate & 512)) {
-                        const int c = lane & 3;
-                        const int tok_g = n0 + half_id * HC + cc + c * 8;    // this lane's 8 tokens
-                        uint32_t goff = (uint32_t)tok_g;                     // their offset inside an output row
-                        if constexpr (CHAIN) {   // 8 images of one output pixel in the consumer's halo-padded plane
-                            if (tok_g < p.N) {
-                                const int pix = tok_g / p.Bp, nn = tok_g - pix * p.Bp;
-                                const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
-                                goff = (uint32_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
+                    if constexpr (!CHAIN) {
+                        __half* dst = obase + roff + tok0;
+                        if (p.wide_stores && !use_c) {                   // N % 16 == 0: 16 tokens are valid as a whole
+                            if (tok0 < p.N) sm100::st_global_32B(dst, v[0], v[1]);
+                            if (tok0 + 16 < p.N) sm100::st_global_32B(dst + 16, v[2], v[3]);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                if (tok0 + c * 8 < p.N) {                // N % 8 == 0: 8 tokens are valid as a whole
+                                    if (use_c) {
+                                        const uint4 cv = *(const uint4*)(p.C + roff + tok0 + c * 8);
+                                        __half* h = (__half*)&v[c];
+                                        const __half* ch = (const __half*)&cv;
+#pragma unroll
+                                        for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
+                                    }
+                                    *(uint4*)(dst + c * 8) = v[c];
+                                }
                             }
                         }
+                    } else {
+                        // 8 consecutive tokens are 8 images of one output pixel; the pixel's place in the
+                        // consumer's halo-padded plane is found once and stepped from group to group
+                        if (tok0 < p.N) {
+                            int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
+                            int oh = pix / p.Wo, ow = pix - oh * p.Wo;
 #pragma unroll
-                        for (int i = 0; i < LR / 8; ++i) {
-                            const int row = i * 8 + (lane >> 2);
-                            uint4 v = *(const uint4*)(tile + row * 64 + ((c ^ ((row >> 1) & 3)) << 4));
-                            if (tok_g < p.N && !(ablate & 8)) {
-                                const size_t off = (size_t)roff[i] + (size_t)goff;
-                                if (use_c) {
-                                    const uint4 cv = *(const uint4*)(p.C + off);
-                                    __half* h = (__half*)&v;
-                                    const __half* ch = (const __half*)&cv;
-#pragma unroll
-                                    for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
-                                }
-                                if constexpr (CHAIN) {   // out = relu(alpha * conv + residual), fp16
-                                    __half2* h = (__half2*)&v;
-                                    if (use_res) {
-                                        const uint4 rv = *(const uint4*)(p.res + (size_t)rres[i] + (size_t)goff);
+                            for (int c = 0; c < 4; ++c) {
+                                if (tok0 + c * 8 < p.N) {
+                                    const size_t goff = (size_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
+                                    __half2* h = (__half2*)&v[c];
+                                    if (use_res) {                       // out = relu(alpha * conv + residual), fp16
+                                        const uint4 rv = *(const uint4*)(p.res + rres + goff);
                                         const __half2* rh = (const __half2*)&rv;
 #pragma unroll
                                         for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], rh[e]);
@@ -796,12 +837,15 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
 #pragma unroll
                                         for (int e = 0; e < 4; ++e) h[e] = __hmax2(h[e], zero2);
                                     }
+                                    *(uint4*)(obase + roff + goff) = v[c];
                                 }
-                                *(uint4*)(obase + off) = v;
+                                nn += 8;
+                                if (nn >= p.Bp) { nn = 0; if (++ow >= p.Wo) { ow = 0; ++oh; } }
                             }
                         }
                     }
-                    __syncwarp();
+                    }
+                    __syncwarp();                                        // the next TMEM load is warp-wide
                 }
                 if (tid == 0) TRACE(2, li, 3);
                 continue;
@@ -972,6 +1016,12 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             }
             if (tid == 0) TRACE(2, li, 3);
         }
+#ifdef SHFLBW_COUNTERS
+        if (lane == 0 && p.trace != nullptr) {   // per epilogue warp: cycles waiting for an accumulator, cycles in the role
+            unsigned long long* o = p.trace + 148 * 48 + (blockIdx.x * 8 + warp) * 2;
+            o[0] = ec_wait; o[1] = clock64() - ec_t0;
+        }
+#endif
         if (tid == 0) CTRACE(4);
     }
 

@@ -475,6 +475,7 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         p.perm = st->perm; p.status_word = st->status_word; p.alpha = st->alpha; p.beta = st->beta;
         p.wait_limit = g_wait_limit; p.inject_from = g_inject_from; p.idx_limit = (unsigned)(st->K - 1);
         p.B = (const __half*)st->B; p.C = (const __half*)st->C; p.D = (__half*)st->D; p.N = st->N;
+        p.wide_stores = (st->N % 16 == 0) && (((uintptr_t)st->D & 31) == 0);
         if (ch.gather != st->gather) return SHFLBW_ERR_INVALID_ARG;
         if (st->gather == shflbw::kGatherTma) std::memcpy(p.tmap_b, st->tmap_b, sizeof p.tmap_b);
         p.num_items = st->num_items; p.tiles_n = st->tiles_n;
@@ -601,7 +602,7 @@ static size_t unperm_smem_bytes(int F) {
 //                   stored filter order -> (with a filter permutation) unpermute_filters.
 //   planes out      relayout -> panel kernel with the filters in TMEM lanes, writing the output
 //                   as planes [F][Ho][Wo][Bp] with plane = LOGICAL channel (the permutation is
-//                   the row index of its stores, free) -> chain_export_nhwc transposes the planes
+//                   the row index of its stores, free) -> planes_to_nhwc transposes the planes
 //                   to NHWC.  Used for V = 64 / 128 filters with enough non-zero columns per
 //                   block: one MMA per 16 columns covers the whole token tile.
 // SHFLBW_CONV_PLANES=0|1 forces the choice (tuning aid).
@@ -638,8 +639,7 @@ int plan_conv(const shflbw_matrix* f, int B, int Hin, int Win, int stride, const
     // planes out?
     PanelChoice ch;
     bool planes = false;
-    const size_t export_smem = (size_t)f->F * 16;
-    const bool planes_possible = (f->brow == 64 || f->brow == 128) && export_smem <= 227 * 1024 &&
+    const bool planes_possible = (f->brow == 64 || f->brow == 128) && f->F / 64 <= 65535 &&
                                  (long long)f->F * tokens < (1ll << 32) - 1;
     if (planes_possible) {
         bool want = padded_cols >= 192ll * row_blocks;      // same rule as the chained layers: >= 3 stages per block
@@ -653,9 +653,6 @@ int plan_conv(const shflbw_matrix* f, int B, int Hin, int Win, int stride, const
     if (planes) {
         out->variant = 1;
         out->staged_out_bytes = (size_t)f->F * (size_t)tokens * 2;
-        if (export_smem > 48 * 1024)
-            CK(cudaFuncSetAttribute((const void*)shflbw::chain_export_nhwc, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    (int)export_smem));
     } else {
         rc = pick_panel<shflbw::kPanelConv>(f->brow, tokens, row_blocks, 0, &ch);
         if (rc != SHFLBW_OK) return rc;
@@ -748,10 +745,9 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     CK(launch(ch.fn, dim3(st->grid_x, st->grid_y), dim3(ch.threads), ch.smem, s, p));
     // 3. back to NHWC in logical channel order.
     if (planes) {
-        const long long blocks = (long long)st->Ho * st->Wo * (st->Bp / 8);
-        CK(launch(shflbw::chain_export_nhwc, dim3((unsigned)blocks), dim3(256), (size_t)st->F * 16, s,
-                  (const __half*)st->staged_out, (__half*)st->ofmap, (const int*)nullptr, st->B, st->Bp, st->Ho, st->Wo,
-                  st->Ho, st->Wo, 0, 0, st->F));
+        const int npix = st->Ho * st->Wo;
+        CK(launch(shflbw::planes_to_nhwc, dim3((unsigned)(((long long)npix * st->Bp + 63) / 64), (unsigned)(st->F / 64)), dim3(256), 0, s,
+                  (const __half*)st->staged_out, (__half*)st->ofmap, st->B, st->Bp, npix, st->F));
     } else if (st->staged_out) {
         const int num_pos = st->B * st->Ho * st->Wo;
         const int per_block = shflbw::kUnpermThreads / shflbw::unperm_threads_per_pos(st->F);

@@ -110,6 +110,12 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst_smem, const void* tmap,
         : "memory");
 }
 
+// 32-byte global store (one whole L2 sector) from two 16-byte registers sets; dst 32-byte aligned.
+__device__ __forceinline__ void st_global_32B(void* dst, const uint4& a, const uint4& b) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w),
+                 "r"(b.x), "r"(b.y), "r"(b.z), "r"(b.w) : "memory");
+}
+
 // ------------------------------------------------------------------ cp.async ----
 // 16-byte global->shared copy through L2 only; src_bytes = 0 zero-fills the destination.
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src, uint32_t src_bytes) {

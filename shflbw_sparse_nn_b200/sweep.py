@@ -19,7 +19,8 @@ shflbw_sparse_nn_b200.sweep resnet50 ...` the batch is split over G GPUs (filter
 exchange) and the per-layer time is the maximum over the ranks.
 
 Timing follows the reference's tool (benchmark/benchmark.spmm.cu:36-49): warm-up launches,
-then the mean over `reps` launches between two CUDA events.  Inputs alternate between buffers
+then the mean over `reps` launches between two CUDA events (the launches replayed from one CUDA
+graph, so that small kernels are not hidden behind the host's launch cost).  Inputs alternate between buffers
 whose total size exceeds the L2 cache.  Peaks come from --hbm-gbs / --tflops (defaults: a measured
 copy bandwidth and dense fp16 tensor throughput of one B200)."""
 from __future__ import annotations
@@ -32,7 +33,7 @@ import numpy as np
 
 SPMM_WEIGHTS = [(3072, 768), (768, 3072), (4096, 4096), (11008, 4096)]
 SPMM_N = [512, 4096, 16384]
-SPMM_V = [32, 64, 128]
+SPMM_V = [16, 32, 64, 128]
 SPMM_DENSITY = [0.05, 0.1, 0.25, 0.5]
 
 # (Hout, Wout, C, F, R, S, stride, uses in one forward pass of the [3,4,6,3] bottleneck stack)
@@ -51,14 +52,33 @@ L2_BYTES = 126 << 20
 
 
 def _time(torch, launches, reps, warmup=5):
+    """Mean seconds per launch: `reps` launches (rotating through `launches`) captured once into a
+    CUDA graph and replayed, so that the host's per-launch cost does not hide kernels of a few
+    microseconds; falls back to plain launches if capture is not possible."""
     s = torch.cuda.current_stream()
     for i in range(warmup):
         launches[i % len(launches)](s)
     torch.cuda.synchronize()
+    run = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(s)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                cap = torch.cuda.current_stream()
+                for i in range(reps):
+                    launches[i % len(launches)](cap)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        run = graph.replay
+    except Exception:
+        torch.cuda.synchronize()
+        run = lambda: [launches[i % len(launches)](s) for i in range(reps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(s)
-    for i in range(reps):
-        launches[i % len(launches)](s)
+    run()
     e1.record(s)
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) * 1e-3 / reps  # seconds
