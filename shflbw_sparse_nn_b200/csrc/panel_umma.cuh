@@ -110,11 +110,16 @@ constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2, kPanelSpmmRow
 //                   tensor map covers this GPU's own B; no multicast), the copy engine applies
 //                   the 128-byte swizzle and completes the stage's barrier by byte count, so the
 //                   producers never wait for data.  SpMM with rows in lanes only.
-constexpr int kGatherCpAsync = 0, kGatherTma = 1;
+//   kGatherCpAsyncArrive  the same 16-byte cp.async copies, but every lane hands its stage to the
+//                   barrier with cp.async.mbarrier.arrive.noinc: the arrival fires when the lane's
+//                   copies have landed, so the producers never wait for data and need no publish
+//                   step; row ids travel in registers (loaded two stages ahead).
+constexpr int kGatherCpAsync = 0, kGatherTma = 1, kGatherCpAsyncArrive = 2;
 
 template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1, int GATHER_ = kGatherCpAsync>
 struct PanelCfg {
     static constexpr bool TMA = GATHER_ == kGatherTma;
+    static constexpr bool ARRIVE = GATHER_ == kGatherCpAsyncArrive;
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
     static constexpr int GROUPS = GROUPS_;                 // producer groups that take the stages in turn
@@ -151,7 +156,7 @@ struct PanelCfg {
     static constexpr int IDX_AHEAD = LAG + 1;              // a group fetches row ids this many of its stages ahead
     static constexpr int IDX_RING = (IDX_AHEAD + 1) * GROUPS <= 8 ? 8 : 16;   // stages of row ids kept in shared memory
     static_assert((IDX_AHEAD + 1) * GROUPS <= IDX_RING, "row-id ring too small");
-    static constexpr int IDX_BYTES = TMA ? 0 : IDX_RING * KS * 4;   // (the TMA gather loads its row ids straight into registers)
+    static constexpr int IDX_BYTES = (TMA || ARRIVE) ? 0 : IDX_RING * KS * 4;   // (the TMA gather loads its row ids straight into registers)
     static constexpr int SMEM_BYTES = PIPE_BYTES + OUT_BYTES + BAR_BYTES + TAB_BYTES + IDX_BYTES + 1024;  // + align slack
     static constexpr bool SWAP = MODE == kPanelSpmmRows || MODE == kPanelConvChainRows;
     static constexpr int KG_BYTES = SWAP ? T * 16 : 2048;   // 8 gathered rows (one K group) of the token tile
@@ -165,7 +170,7 @@ struct PanelCfg {
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
     static_assert(KS % 16 == 0 && PW % GROUPS == 0 && KS % (PW / GROUPS) == 0 && (KS / (PW / GROUPS)) % (32 / (T / 8)) == 0,
                   "rows per producer warp");
-    static_assert(LAG >= 1 && LAG <= 2 && (TMA || STAGES > GROUPS * LAG), "publish lag");
+    static_assert(LAG >= 1 && LAG <= 2 && (TMA || ARRIVE || STAGES > GROUPS * LAG), "publish lag");
     static_assert(SMEM_BYTES <= 227 * 1024, "shared memory budget");
 };
 
@@ -233,7 +238,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             // per thread, i.e. more than the copies themselves.
             // cp.async gather: one arrival per producer WARP of the group.  TMA gather: one arrival
             // (with the stage's byte count) by the group's first warp.
-            sm100::mbar_init(&full_bar[s], Cfg::TMA ? 1 : PW / Cfg::GROUPS);
+            // Deferred arrivals: one per LANE of the group's warps.
+            sm100::mbar_init(&full_bar[s], Cfg::TMA ? 1 : Cfg::ARRIVE ? (PW / Cfg::GROUPS) * 32 : PW / Cfg::GROUPS);
             sm100::mbar_init(&empty_bar[s], 1);   // one tcgen05.commit per drain
         }
         for (int b = 0; b < 2; ++b) {
@@ -366,6 +372,137 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             }
         }
     tma_producer_done:;
+#ifdef SHFLBW_COUNTERS
+        if (lane == 0 && p.trace != nullptr && pidx < 8) {
+            unsigned long long* o = p.trace + 148 * 16 + (blockIdx.x * 8 + pidx) * 4;
+            o[0] = pc_empty; o[1] = pc_n; o[2] = clock64() - pc_t0;
+        }
+#endif
+        }
+    } else if (warp >= 9 && Cfg::ARRIVE) {
+        // ------------------------------------- producers (cp.async, deferred arrivals) ----
+        // The GW warps of a group share a stage (RPW rows each); a warp instruction copies RPI
+        // rows of the token tile, 16 bytes per lane, straight into the swizzled layout.  After its
+        // copies of a stage every lane issues cp.async.mbarrier.arrive.noinc on the stage's
+        // barrier: the arrival is delivered when that lane's copies have landed.  Nothing here
+        // waits for data; the only wait is for a free stage.  (The consumer orders the generic-
+        // proxy writes before the tensor core's reads with a proxy fence after its own wait.)
+        if constexpr (Cfg::ARRIVE) {
+        constexpr int GROUPS = Cfg::GROUPS, GW = PW / GROUPS, RPW = KS / GW;
+        constexpr int CPR = T / 8, RPI = 32 / CPR, NQ = RPW / RPI;
+        constexpr int XT = NQ < 8 / RPI ? NQ : 8 / RPI;
+        static_assert((RPW % 8 == 0 || 8 % RPW == 0) && RPW <= 32, "rows per producer warp");
+        const int grp = pidx / GW, pw = pidx % GW;
+        const int chunk = lane % CPR;
+        const int sub = RPI == 2 ? (lane >> 4) : 0;
+        const int rbase = pw * RPW + sub;
+        const uint32_t gbase = SWAP ? (uint32_t)((pw * RPW / 8) * Cfg::KG_BYTES + (chunk >> 3) * 1024)
+                                    : (uint32_t)((chunk >> 4) * Cfg::G_ACC + (pw * RPW / 8) * 2048 + (((chunk & 15) >> 3)) * 1024);
+        uint32_t gx[XT];
+#pragma unroll
+        for (int j = 0; j < XT; ++j) {
+            const int r7 = (pw * RPW + j * RPI + sub) & 7;
+            gx[j] = (uint32_t)(r7 * 128 + (((chunk & 7) ^ r7) << 4));
+        }
+        struct Cursor { int li, kt, num_k, row_begin, rows_total; };
+        auto enter = [&](Cursor& c) {
+            c.kt = 0;
+            while (c.li < nloc) {
+                const int2 e = item_tab[c.li];
+                c.row_begin = e.x; c.rows_total = e.y; c.num_k = (e.y + KS - 1) / KS;
+                if (c.num_k > 0) return;
+                ++c.li;
+            }
+            c.num_k = 0; c.row_begin = 0; c.rows_total = 0;
+        };
+        auto advance = [&](Cursor& c) { if (++c.kt >= c.num_k) { ++c.li; enter(c); } };
+        // Lane j < RPW holds the id of row pw*RPW + j of a stage (for SpConv: its element offset);
+        // ids are loaded two of the group's stages ahead and handed out by shuffle.
+        auto load_id = [&](const Cursor& c) {
+            int v = 0;
+            const int r = c.kt * KS + pw * RPW + lane;
+            if (lane < RPW && c.li < nloc && r < c.rows_total) v = __ldg(p.blk_idx + c.row_begin + r);
+            if constexpr (CONV)
+                return (int)min((unsigned)(((v & 0xffff) * (p.Hp * p.Wp) + ((v >> 16) & 0xff) * p.Wp + ((v >> 24) & 0xff)) * p.Bp), p.idx_limit);
+            else
+                return (int)min((unsigned)v, p.idx_limit);
+        };
+        Cursor pre{0, 0, 0, 0, 0};
+        enter(pre);
+        for (int d = 0; d < grp; ++d) advance(pre);
+        int id_cur = load_id(pre);
+        for (int g = 0; g < GROUPS; ++g) advance(pre);
+        int id_next = load_id(pre);
+        for (int g = 0; g < GROUPS; ++g) advance(pre);
+        int it = 0;
+#ifdef SHFLBW_COUNTERS
+        long long pc_empty = 0, pc_n = 0, pc_t0 = clock64();
+#endif
+        for (int li = 0; li < nloc; ++li) {
+            const int2 ent = item_tab[li];
+            const int num_k = (ent.y + KS - 1) / KS;
+            if (num_k == 0) continue;
+            const int item = (int)blockIdx.x + li * (int)gridDim.x;
+            const int tok0 = (item % p.tiles_n) * T + chunk * 8;
+            const bool chunk_ok = tok0 < p.N;
+            const uint32_t nbytes = chunk_ok ? 16u : 0u;
+            const __half* conv_src0 = p.Xs;
+            if constexpr (CONV) {
+                if (chunk_ok) {
+                    const int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
+                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                    conv_src0 = p.Xs + ((oh * p.stride * p.Wp + ow * p.stride) * p.Bp + nn);
+                }
+            }
+            const __half* lane_src0 = chunk_ok ? p.B + tok0 : p.B;
+            const uint32_t row_pitch = chunk_ok ? (uint32_t)p.N : 0u;
+            const __half* wsrc = p.blk_val + (size_t)ent.x * V;
+            for (int kt = 0; kt < num_k; ++kt, ++it) {
+                if ((it % GROUPS) != grp) continue;
+                const int s = it % STAGES;
+                if (it >= STAGES) {
+#ifdef SHFLBW_COUNTERS
+                    const long long e0c = clock64();
+#endif
+                    int ok = 1;
+                    if (lane == 0)
+                        ok = sm100::mbar_wait_bounded(&empty_bar[s], ((it / STAGES) - 1) & 1, cta_abort, p.status_word,
+                                                      SHFLBW_DEVSTAT_TIMEOUT_EMPTY, p.wait_limit, 32);
+                    if (!__shfl_sync(0xffffffffu, ok, 0)) goto arrive_producer_done;
+#ifdef SHFLBW_COUNTERS
+                    pc_empty += clock64() - e0c; ++pc_n;
+#endif
+                }
+                const int rows_valid = min(KS, ent.y - kt * KS);
+                const uint32_t st_base = smem_base + s * Cfg::STAGE_BYTES;
+                if (pw == 0 && lane == 0 && !(ablate & 4)) {
+                    const uint32_t wbytes = (uint32_t)(rows_valid * V * 2);
+                    sm100::mbar_expect_tx(&full_bar[s], wbytes);
+                    sm100::bulk_copy_g2s(st_base + (uint32_t)Cfg::G_BYTES, wsrc + (size_t)kt * KS * V, wbytes, &full_bar[s]);
+                }
+                int idq[NQ];
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) idq[q] = __shfl_sync(0xffffffffu, id_cur, q * RPI + sub);
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) {
+                    if (rbase + q * RPI < rows_valid && !(ablate & 2)) {
+                        const uint32_t dst = st_base + gbase + (uint32_t)(((q * RPI) >> 3) * Cfg::KG_BYTES) + gx[q % XT];
+                        if constexpr (CONV) sm100::cp_async_16(dst, conv_src0 + idq[q], nbytes);
+                        else sm100::cp_async_16(dst, lane_src0 + (uint64_t)(uint32_t)idq[q] * row_pitch, nbytes);
+                    }
+                }
+#ifdef SHFLBW_FAULT_INJECT
+                if (!(p.inject_from >= 0 && it >= p.inject_from && pidx == 0))   // the withheld arrivals
+#endif
+                sm100::cp_async_arrive_noinc(&full_bar[s]);
+                id_cur = id_next;
+                id_next = load_id(pre);
+                for (int g = 0; g < GROUPS; ++g) advance(pre);
+            }
+        }
+    arrive_producer_done:
+        sm100::cp_async_commit();
+        sm100::cp_async_wait<0>();          // nothing of this warp is in flight when the block ends
 #ifdef SHFLBW_COUNTERS
         if (lane == 0 && p.trace != nullptr && pidx < 8) {
             unsigned long long* o = p.trace + 148 * 16 + (blockIdx.x * 8 + pidx) * 4;

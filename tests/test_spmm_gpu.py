@@ -255,3 +255,33 @@ def test_host_buffer_call_pipelines_wide_operands_in_column_chunks():
     D_dev, _ = run_spmm(m, N, B, alpha=0.5, Cm=Cm, beta=2.0)
     # same kernels on the same columns: only the summation order of a token tile's partners differs -> none
     assert_close_fp16(D_host, D_dev.astype(np.float32), what="chunked host call vs device call")
+
+
+@pytest.mark.parametrize("N", [1000, 264, 64])
+def test_tma_tile_gather_kernel(N, monkeypatch):
+    """The SpMM kernel whose producers fetch the rows of B with TMA tile::gather4 (the default for
+    64-row blocks once every SM has a few 256-token items; forced here on small shapes): ragged
+    dense width (the copy engine zero-fills past N), empty and short row blocks, alpha, and
+    beta * C; bit-identical to the cp.async kernel, which sums in the same order."""
+    monkeypatch.setenv("SHFLBW_SWAP", "1")
+    M, K, V = 256, 640, 64
+    counts = [0, 1, 130, 47]
+    rng = np.random.default_rng(N)
+    indptr = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+    indices = np.concatenate([np.sort(rng.choice(K, c, replace=False)) for c in counts]).astype(np.int32)
+    m = sb.BlockwiseSpMatrix.from_arrays(M, K, V, indptr, indices, sb.uniform_half(3, indices.size * V),
+                                         rng.permutation(M).astype(np.int32))
+    B = sb.uniform_half(901 + N, K * N).reshape(K, N)
+    Cm = sb.uniform_half(902, M * N).reshape(M, N)
+    monkeypatch.setenv("SHFLBW_GATHER", "1")
+    D1, op1 = run_spmm(m, N, B, tokens=256)
+    D2, op2 = run_spmm(m, N, B, alpha=0.5, Cm=Cm, beta=-1.5, tokens=256)
+    assert op1._state.gather == 1 and op2._state.gather == 1 and op1._state.variant == 1
+    monkeypatch.setenv("SHFLBW_GATHER", "0")
+    E1, op3 = run_spmm(m, N, B, tokens=256)
+    E2, _ = run_spmm(m, N, B, alpha=0.5, Cm=Cm, beta=-1.5, tokens=256)
+    assert op3._state.gather == 0
+    assert_close_fp16(D1, _oracle(m, N, B), what=f"TMA gather N={N}")
+    assert_close_fp16(D2, _oracle(m, N, B, 0.5, Cm, -1.5), what=f"TMA gather N={N} alpha/beta")
+    assert np.array_equal(D1.view(np.uint16), E1.view(np.uint16)) and np.array_equal(D2.view(np.uint16), E2.view(np.uint16))
+
