@@ -231,6 +231,12 @@ def run_ours(args):
     lib = _cabi.lib()
 
     pk = peaks()
+    if args.only == "spconv":       # profiling aid: the SpConv loop alone
+        out = {"spconv": bench_spconv(sb, torch, dist, pk, steps=args.steps, warmup=max(3, args.warmup), use_graph=not args.no_graph)}
+        dist.close()
+        if rank == 0:
+            print(json.dumps(out))
+        return
     m = build_problem(sb)
     m.transform_and_sync_device()
     nnzb, X = m.nnzb, M_ // V_
@@ -633,6 +639,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every timed step from the host instead of replaying a CUDA graph")
     ap.add_argument("--quick", action="store_true",
                     help="profiling aid: timed SpMM loop plus a short SpConv loop only (no stack, no e2e, no reference kernels, no CPU baseline)")
+    ap.add_argument("--only", default="", choices=["", "spconv"],
+                    help="profiling aid: run just this part (spconv: the headline SpConv loop with --steps calls)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

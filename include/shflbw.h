@@ -160,7 +160,7 @@ typedef struct shflbw_spmm_state {
     int tokens_per_cta;      /* dense-dimension tile of one work item */
     int stages;              /* shared-memory pipeline depth */
     int producer_warps;      /* warps issuing the gather */
-    int variant;             /* pipeline-shape variant (0 = default) */
+    int variant;             /* 0: tokens in TMEM lanes; 1: rows of the block in TMEM lanes */
     int num_items, tiles_n;  /* work items = row blocks x dense tiles */
     unsigned grid_x, grid_y, block_x;
     size_t shared_mem_size;
@@ -221,7 +221,7 @@ typedef struct shflbw_spconv_state {
     int tokens_per_cta;
     int stages;
     int producer_warps;
-    int variant;
+    int variant;             /* 0: tokens in TMEM lanes; 1: filters in TMEM lanes (NHWC calls: planes out + transpose) */
     int num_items, tiles_n;
     unsigned grid_x, grid_y, block_x;
     size_t shared_mem_size;
@@ -230,7 +230,8 @@ typedef struct shflbw_spconv_state {
     const void* ifmap;       /* NHWC input (device)  */
     void* ofmap;             /* NHWC output (device) */
     void* staged_in;         /* scratch: input as [C][Hin+R-1][Win+S-1][Bp], zero halo */
-    void* staged_out;        /* scratch: [B*Ho*Wo][F] in stored filter order, or NULL  */
+    void* staged_out;        /* scratch: output planes [F][Ho][Wo][Bp] (variant 1), [B*Ho*Wo][F] in stored
+                                filter order (variant 0, permuted filter), or NULL */
     size_t staged_in_bytes, staged_out_bytes;
     const int* blk_ptr;
     const int* blk_idx;      /* tensor-core path: ids decoded as c | r<<16 | s<<24 */
@@ -317,19 +318,22 @@ int shflbw_spconv_chain_set_residual(shflbw_matrix_t* filter, shflbw_spconv_stat
 /* SpConv for callers that must not allocate.  No counterpart in the reference project.
  *
  * Some hosts call this library from a place where device allocation is off limits: the
- * execute hook of an inference-runtime plugin, a serving loop whose memory is carved up
+ * execute hook of an inference-runtime plugin, or a serving loop whose memory is carved up
  * front by a pool (a late cudaMalloc would synchronise the whole device and can fail when
- * the pool owns the GPU), or code that is being recorded for later replay.  The regular
- * shflbw_spconv_init grows scratch buffers with cudaMalloc; this entry point does not.  It
- * runs the same three kernels (relayout, panel kernel, inverse filter permutation) with
- * their scratch in a fixed array of SHFLBW_STATIC_SCRATCH_BYTES that is part of the
- * library image; every GPU that loads the library holds that array until the process exits.
+ * the pool owns the GPU).  The regular shflbw_spconv_init grows scratch buffers with
+ * cudaMalloc; this entry point does not.  It runs the same kernels (relayout, panel kernel,
+ * transpose or inverse filter permutation) with their scratch in a fixed array of
+ * SHFLBW_STATIC_SCRATCH_BYTES that is part of the library image; every GPU that loads the
+ * library holds that array until the process exits.
  *
  *  - `filter` must already be on the device (shflbw_matrix_to_device, done at set-up time).
  *  - ifmap / ofmap are NHWC device pointers exactly as for shflbw_spconv_init; the launch is
  *    asynchronous on `stream`.
- *  - Needs 2*C*(Hin+R-1)*(Win+S-1)*roundup8(B) bytes, plus 2*B*Ho*Wo*F when the filter is
- *    permuted, each rounded up to 256.  More than the capacity -> SHFLBW_ERR_TOO_LARGE, nothing is launched.
+ *  - Needs 2*C*(Hin+R-1)*(Win+S-1)*roundup8(B) bytes for the staged input, plus up to
+ *    2*roundup8(B)*Ho*Wo*F for the staged output (not needed by unpermuted filters on the
+ *    positions-out plan), each rounded up to 256.  More than the capacity ->
+ *    SHFLBW_ERR_TOO_LARGE, nothing is launched.  The 32-bit range checks of shflbw_spconv_init
+ *    apply as well (SHFLBW_ERR_UNSUPPORTED).
  *  - The first call on each device looks up the array's device address; make that first
  *    call during set-up, before any stream capture on that device.
  *  - All calls on a device share the one array and it keeps the previous call's contents.

@@ -865,16 +865,24 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const int n0 = (item % p.tiles_n) * T;
             const bool has_k = item_tab[li].y > 0 && !(ablate & 1);
             const int b = li & 1;
-            int acc_ok = 1;
-            if (lane == 0)
-                acc_ok = sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
-                                                  SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 32);
-            if (!__shfl_sync(0xffffffffu, acc_ok, 0)) break;    // timed out or aborted: store nothing more
-            sm100::tc_fence_after_sync();
+            // Wait for the item's accumulator (one lane polls, the warp follows).  false: the wait
+            // timed out or the block is aborting -- store nothing more.
+            auto wait_accumulator = [&]() -> bool {
+                int acc_ok = 1;
+                if (lane == 0)
+                    acc_ok = sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
+                                                      SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 32);
+                if (!__shfl_sync(0xffffffffu, acc_ok, 0)) return false;
+                sm100::tc_fence_after_sync();
 #ifdef SHFLBW_COUNTERS
-            ec_wait += clock64() - ew0;
+                ec_wait += clock64() - ew0;
 #endif
-            if (tid == 0) TRACE(2, li, 0);
+                if (tid == 0) TRACE(2, li, 0);
+                return true;
+            };
+            if constexpr (SWAP || !ROWS_OUT) {
+                if (!wait_accumulator()) break;
+            }
             if constexpr (SWAP) {
                 // Rows in lanes: lane l of quadrant `quad` holds output row m of the block (V = 64:
                 // the quadrant's first 16 lanes, m = 16*quad + l; V = 128: all 32, m = 32*quad + l)
@@ -906,6 +914,36 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                 const bool use_c = !CHAIN && p.beta != 0.0f && p.C != nullptr;
 #pragma unroll 1
                 for (int cc = 0; cc < HC; cc += 32) {
+                    const int tok0 = n0 + half_id * HC + cc;             // this lane's 32 tokens start here
+                    // Where the four 8-token groups go, and (chained layers) the residual that gets added
+                    // to them: requested before the accumulator read, so that the global-memory latency
+                    // hides behind it.
+                    size_t goffs[4];
+                    uint4 addend[4];
+                    if (lane < LR) {
+                        if constexpr (CHAIN) {
+                            // 8 consecutive tokens are 8 images of one output pixel; the pixel's place in the
+                            // consumer's halo-padded plane is found once and stepped from group to group
+                            int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
+                            int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                goffs[c] = (size_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
+                                nn += 8;
+                                if (nn >= p.Bp) { nn = 0; if (++ow >= p.Wo) { ow = 0; ++oh; } }
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) goffs[c] = (size_t)(tok0 + c * 8);   // (folds into the addresses)
+                        }
+                        if constexpr (CHAIN) {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                addend[c] = make_uint4(0u, 0u, 0u, 0u);
+                                if (use_res && tok0 + c * 8 < p.N) addend[c] = *(const uint4*)(p.res + rres + goffs[c]);
+                            }
+                        }
+                    }
                     uint32_t r[32];
                     if (has_k) {
                         sm100::tmem_ld_32x32b_x32(acc0 + cc, r);
@@ -921,7 +959,6 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                         if (tid == 0) TRACE(2, li, 1);
                     }
                     if (lane < LR && !(ablate & 520)) {
-                    const int tok0 = n0 + half_id * HC + cc;             // this lane's 32 tokens start here
                     uint4 v[4];
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -942,7 +979,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
 #pragma unroll
                             for (int c = 0; c < 4; ++c) {
                                 if (tok0 + c * 8 < p.N) {                // N % 8 == 0: 8 tokens are valid as a whole
-                                    if (use_c) {
+                                    if (use_c) {                         // (the rare beta != 0 case pays the load's latency here)
                                         const uint4 cv = *(const uint4*)(p.C + roff + tok0 + c * 8);
                                         __half* h = (__half*)&v[c];
                                         const __half* ch = (const __half*)&cv;
@@ -954,30 +991,20 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                             }
                         }
                     } else {
-                        // 8 consecutive tokens are 8 images of one output pixel; the pixel's place in the
-                        // consumer's halo-padded plane is found once and stepped from group to group
-                        if (tok0 < p.N) {
-                            int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
-                            int oh = pix / p.Wo, ow = pix - oh * p.Wo;
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) {
-                                if (tok0 + c * 8 < p.N) {
-                                    const size_t goff = (size_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
-                                    __half2* h = (__half2*)&v[c];
-                                    if (use_res) {                       // out = relu(alpha * conv + residual), fp16
-                                        const uint4 rv = *(const uint4*)(p.res + rres + goff);
-                                        const __half2* rh = (const __half2*)&rv;
+                        for (int c = 0; c < 4; ++c) {
+                            if (tok0 + c * 8 < p.N) {
+                                __half2* h = (__half2*)&v[c];
+                                if (use_res) {                           // out = relu(alpha * conv + residual), fp16
+                                    const __half2* rh = (const __half2*)&addend[c];
 #pragma unroll
-                                        for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], rh[e]);
-                                    }
-                                    if (p.relu) {
-#pragma unroll
-                                        for (int e = 0; e < 4; ++e) h[e] = __hmax2(h[e], zero2);
-                                    }
-                                    *(uint4*)(obase + roff + goff) = v[c];
+                                    for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], rh[e]);
                                 }
-                                nn += 8;
-                                if (nn >= p.Bp) { nn = 0; if (++ow >= p.Wo) { ow = 0; ++oh; } }
+                                if (p.relu) {
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) h[e] = __hmax2(h[e], zero2);
+                                }
+                                *(uint4*)(obase + roff + goffs[c]) = v[c];
                             }
                         }
                     }
@@ -1032,10 +1059,36 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                 }
             }
             const __half2 zero2 = __float2half2_rn(0.f);
-#pragma unroll 1
-            for (int cc = 0; cc < COLS; cc += CW) {
+            // What gets added to the product (beta * C, or the residual of a chained layer) does not
+            // depend on the accumulator: the addends of the item's first two chunks are requested
+            // BEFORE waiting for it, each later chunk's two chunks ahead, so that their global-memory
+            // latency is off the critical path (these layers are often all epilogue).
+            constexpr int NCH = COLS / CW;
+            const bool add_res = MODE == kPanelConvChain && p.res != nullptr;
+            const bool need_add = ok_g && (use_c || add_res);
+            uint4 addend[2][4];
+            auto fetch_addend = [&](int cc, uint4 (&dst)[4]) {
+#pragma unroll
+                for (int i = 0; i < CW / 8; ++i) {
+                    const int m = mbase + cc + 8 * i + (lane >> 2);
+                    if (use_c) {
+                        const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
+                        dst[i] = *(const uint4*)(p.C + (size_t)((uint32_t)row * (uint32_t)p.N) + (size_t)goff);
+                    } else {
+                        const uint32_t rr = (uint32_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (uint32_t)p.out_plane;
+                        dst[i] = *(const uint4*)(p.res + (size_t)rr + (size_t)goff);
+                    }
+                }
+            };
+            if (need_add) {
+                fetch_addend(0, addend[0]);
+                if constexpr (NCH > 1) fetch_addend(CW, addend[1]);
+            }
+            if (!wait_accumulator()) break;
+#pragma unroll
+            for (int ch = 0; ch < NCH; ++ch) {
+                const int cc = ch * CW;
                 uint32_t roff[4];                                        // D offsets of rows cc + 8i + lane/4
-                uint32_t rres[4] = {0u, 0u, 0u, 0u};                     // chained: residual offsets of those rows
 #pragma unroll
                 for (int i = 0; i < CW / 8; ++i) {
                     const int m = mbase + cc + 8 * i + (lane >> 2);
@@ -1045,7 +1098,6 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                     } else {
                         const int plane = (p.out_logical && p.perm) ? __ldg(p.perm + blk * V + m) : blk * V + m;
                         roff[i] = (uint32_t)plane * (uint32_t)p.out_plane;           // stored (chained) or logical order
-                        if (p.res) rres[i] = (uint32_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (uint32_t)p.out_plane;
                     }
                 }
                 {
@@ -1081,17 +1133,15 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                         if (ok_g) {
                             const size_t off = (size_t)roff[i] + (size_t)goff;
                             if (use_c) {
-                                const uint4 cv = *(const uint4*)(p.C + off);
                                 __half* h = (__half*)&v;
-                                const __half* ch = (const __half*)&cv;
+                                const __half* cadd = (const __half*)&addend[ch & 1][i];
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(ch[e], beta1));
+                                for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(cadd[e], beta1));
                             }
                             if constexpr (MODE == kPanelConvChain) {   // out = relu(alpha * conv + residual), fp16
                                 __half2* h = (__half2*)&v;
-                                if (p.res) {
-                                    const uint4 rv = *(const uint4*)(p.res + (size_t)rres[i] + (size_t)goff);
-                                    const __half2* rh = (const __half2*)&rv;
+                                if (add_res) {
+                                    const __half2* rh = (const __half2*)&addend[ch & 1][i];
 #pragma unroll
                                     for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], rh[e]);
                                 }
@@ -1104,6 +1154,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                         }
                     }
                 }
+                if (need_add && ch + 2 < NCH) fetch_addend(cc + 2 * CW, addend[ch & 1]);
                 __syncwarp();
             }
             } else {
