@@ -140,6 +140,12 @@ struct PanelCfg {
     static constexpr int REGS_EPI_RAW = (65536 - (WARPS - 8) * 32 * REGS_LEAN) / 256 / 8 * 8;
     static constexpr int REGS_EPI = REGS_EPI_RAW > 160 ? 160 : REGS_EPI_RAW;
     static_assert(!REG_SPLIT || REGS_EPI >= 88, "epilogue register budget");
+    // Only the 32-warp block is used with the split: 1024 threads x 64 registers is exactly the
+    // register file, so what the lean warpgroups return is exactly what the epilogue's increase
+    // asks for.  (24-warp blocks launched at 80 registers were seen to block in setmaxnreg.inc:
+    // the allocation granularity leaves less in the pool than the arithmetic says, and that wait
+    // has no time limit.)
+    static_assert(!REG_SPLIT || WARPS == 32, "register split: 32-warp blocks only");
     static constexpr int G_ACC = KS * 256;                 // gathered tile of one accumulator: [KS][128] fp16
     static constexpr int G_BYTES = TM * G_ACC;
     static constexpr int W_BYTES = KS * V * 2;

@@ -159,7 +159,6 @@ bool tuned_shape(PanelChoice* out) {
         case 822:  *out = choice<64, 2, 64, 5, 8, MODE, 2, 2>(); return true;
         case 811:  *out = choice<64, 2, 64, 5, 8, MODE, 1, 1>(); return true;
         case 812:  *out = choice<64, 2, 64, 5, 8, MODE, 1, 2>(); return true;
-        case 1231: *out = choice<64, 2, 64, 5, 12, MODE, 3, 1>(); return true;
         case 1621: *out = choice<64, 2, 64, 5, 16, MODE, 2, 1>(); return true;
         case 1622: *out = choice<64, 2, 64, 5, 16, MODE, 2, 2>(); return true;
         case 1611: *out = choice<64, 2, 64, 5, 16, MODE, 1, 1>(); return true;
@@ -183,6 +182,7 @@ bool tuned_shape(PanelChoice* out) {
             case 1610: *out = choice<64, 2, 64, 5, 16, MODE, 1, 1, shflbw::kGatherTma>(); return true;
             case 1620: *out = choice<64, 2, 64, 5, 16, MODE, 2, 1, shflbw::kGatherTma>(); return true;
             case 1640: *out = choice<64, 2, 64, 5, 16, MODE, 4, 1, shflbw::kGatherTma>(); return true;
+            case 840:  *out = choice<64, 2, 64, 5, 8, MODE, 4, 1, shflbw::kGatherTma>(); return true;
             default: break;
         }
     }
