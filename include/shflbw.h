@@ -7,7 +7,8 @@
  *
  * Data conventions (all fp16 arrays are IEEE binary16 passed as uint16_t / void*):
  *   sparse matrix A: M x K, rows grouped in blocks of V = brow consecutive *stored* rows
- *     that share one sorted list of non-zero columns (bcol == 1):
+ *     that share one sorted list of non-zero columns (bcol == 1; wider blocks:
+ *     shflbw_matrix_create_from_block_arrays):
  *       indptr[M/V + 1]   offsets into indices, in non-zero columns
  *       indices[nnzb]     column ids, ascending inside each row block
  *       values[nnzb * V]  values[p*V + m] = A_stored[blk*V + m][indices[p]]
@@ -84,7 +85,7 @@ int shflbw_set_wait_limit_cycles(long long cycles);
 
 /* Replaces BlockwiseSpMatrix<half>::init_random (block_sparse/spmm/blockwise_format.h:70-123)
  * and random_mask (block_sparse/util/random_mask.cc:10-67): mask, permutation, values,
- * achieved density, config string.  bcol must be 1.  stream seed for UNIFORM values = seed. */
+ * achieved density, config string.  ncol % bcol must be 0.  stream seed for UNIFORM values = seed. */
 int shflbw_matrix_create_random(int nrow, int ncol, int brow, int bcol, float density,
                                 int row_permute, unsigned seed, int value_mode,
                                 shflbw_matrix_t** out);
@@ -101,6 +102,15 @@ int shflbw_filter_create_random(int F, int R, int S, int C, int brow, int bcol, 
 int shflbw_matrix_create_from_arrays(int nrow, int ncol, int brow, int nnzb, const int* indptr,
                                      const int* indices, const uint16_t* values, const int* perm,
                                      shflbw_matrix_t** out);
+/* The same with brow x bcol blocks (the format of blockwise_format.h:13-68 in full): indices
+ * are in units of bcol columns, values hold nnzb * brow * bcol halves, each block column by
+ * column (value (mm, kk) of block p at values[p*brow*bcol + kk*brow + mm], :286-297).  The
+ * reference's kernels assert bcol == 1 (spmm/blockwise_op.h:86); here the device image lists a
+ * block's bcol columns one after the other, so every operator accepts such a matrix. */
+int shflbw_matrix_create_from_block_arrays(int nrow, int ncol, int brow, int bcol, int nnzb,
+                                           const int* indptr, const int* indices,
+                                           const uint16_t* values, const int* perm,
+                                           shflbw_matrix_t** out);
 /* Marks a matrix as a conv filter of shape F x R x S x C (nrow == F, ncol == R*S*C). */
 int shflbw_matrix_set_filter_shape(shflbw_matrix_t* m, int F, int R, int S, int C);
 

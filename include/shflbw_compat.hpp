@@ -91,7 +91,7 @@ protected:
         row_permute = shflbw_matrix_row_permute(handle) != 0;
         indptr.assign(shflbw_matrix_indptr(handle), shflbw_matrix_indptr(handle) + nrow / brow + 1);
         indices.assign(shflbw_matrix_indices(handle), shflbw_matrix_indices(handle) + nnzb);
-        values.resize((size_t)nnzb * brow);
+        values.resize((size_t)nnzb * brow * bcol);
         if (nnzb) std::char_traits<char>::copy((char*)values.data(), (const char*)shflbw_matrix_values(handle),
                                                values.size() * 2);
         row_permute_ids.clear();

@@ -26,14 +26,14 @@
 namespace {
 template <class M>
 void fill_from_arrays(M& m, int nrow, int ncol, int brow, int nnzb, const int* indptr,
-                      const int* indices, const uint16_t* values, const int* perm) {
-    m.nrow = nrow; m.ncol = ncol; m.brow = brow; m.bcol = 1; m.nnzb = nnzb;
+                      const int* indices, const uint16_t* values, const int* perm, int bcol = 1) {
+    m.nrow = nrow; m.ncol = ncol; m.brow = brow; m.bcol = bcol; m.nnzb = nnzb;
     m.seed = 0; m.row_permute = perm != nullptr;
-    m.density = (float)nnzb / (nrow / brow) / ncol;
+    m.density = (float)nnzb / (nrow / brow) / (ncol / bcol);
     m.indptr.assign(indptr, indptr + nrow / brow + 1);
     m.indices.assign(indices, indices + nnzb);
-    m.values.resize((size_t)nnzb * brow);
-    std::memcpy((void*)m.values.data(), values, (size_t)nnzb * brow * 2);
+    m.values.resize((size_t)nnzb * brow * bcol);
+    std::memcpy((void*)m.values.data(), values, (size_t)nnzb * brow * bcol * 2);
     if (perm) m.row_permute_ids.assign(perm, perm + nrow); else m.row_permute_ids.clear();
     m.initialized = true;
 }
@@ -96,13 +96,14 @@ int64_t ref_matrix_meta_image(void* h, int* out, int64_t cap_ints) {
     return n;
 }
 
-// Unmodified get_host_reference on caller-provided arrays (single-threaded, as shipped).
-void ref_spmm_host_reference(int M, int K, int N, int brow, int nnzb, const int* indptr,
-                             const int* indices, const uint16_t* values, const int* perm,
-                             const uint16_t* B, float alpha, const uint16_t* C, float beta,
-                             float* D_ref) {
+// Unmodified get_host_reference on caller-provided arrays (single-threaded, as shipped);
+// brow x bcol blocks, indices in units of bcol columns.
+void ref_spmm_host_reference_blocks(int M, int K, int N, int brow, int bcol, int nnzb, const int* indptr,
+                                    const int* indices, const uint16_t* values, const int* perm,
+                                    const uint16_t* B, float alpha, const uint16_t* C, float beta,
+                                    float* D_ref) {
     BlockwiseSpMatrix<half> m;
-    fill_from_arrays(m, M, K, brow, nnzb, indptr, indices, values, perm);
+    fill_from_arrays(m, M, K, brow, nnzb, indptr, indices, values, perm, bcol);
     std::vector<half> Bh = as_half(B, (size_t)K * N);
     std::vector<half> Ch((size_t)M * N);
     if (C) std::memcpy((void*)Ch.data(), C, (size_t)M * N * 2);
@@ -112,19 +113,34 @@ void ref_spmm_host_reference(int M, int K, int N, int brow, int nnzb, const int*
     std::memcpy(D_ref, D.data(), D.size() * 4);
 }
 
+void ref_spmm_host_reference(int M, int K, int N, int brow, int nnzb, const int* indptr,
+                             const int* indices, const uint16_t* values, const int* perm,
+                             const uint16_t* B, float alpha, const uint16_t* C, float beta,
+                             float* D_ref) {
+    ref_spmm_host_reference_blocks(M, K, N, brow, 1, nnzb, indptr, indices, values, perm, B, alpha, C, beta, D_ref);
+}
+
 // Unmodified conv get_host_reference; feature maps in the reference's own layouts
 // (input [C][H][W][B], output [F][H][W][B]).
-void ref_spconv_host_reference(int Bn, int H, int W, int C, int F, int R, int S, int stride,
-                               int brow, int nnzb, const int* indptr, const int* indices,
-                               const uint16_t* values, const int* perm, const uint16_t* ifmap,
-                               float* ofmap_ref) {
+void ref_spconv_host_reference_blocks(int Bn, int H, int W, int C, int F, int R, int S, int stride,
+                                      int brow, int bcol, int nnzb, const int* indptr, const int* indices,
+                                      const uint16_t* values, const int* perm, const uint16_t* ifmap,
+                                      float* ofmap_ref) {
     BlockwiseSpFilter<half> f;
-    fill_from_arrays(f, F, R * S * C, brow, nnzb, indptr, indices, values, perm);
+    fill_from_arrays(f, F, R * S * C, brow, nnzb, indptr, indices, values, perm, bcol);
     f.F = F; f.C = C; f.R = R; f.S = S;
     std::vector<half> X = as_half(ifmap, (size_t)Bn * H * W * C);
     std::vector<float> O((size_t)Bn * H * W * F);
     get_host_reference<half>(f, Bn, H, W, stride, X, O, filter_channel_first);
     std::memcpy(ofmap_ref, O.data(), O.size() * 4);
+}
+
+void ref_spconv_host_reference(int Bn, int H, int W, int C, int F, int R, int S, int stride,
+                               int brow, int nnzb, const int* indptr, const int* indices,
+                               const uint16_t* values, const int* perm, const uint16_t* ifmap,
+                               float* ofmap_ref) {
+    ref_spconv_host_reference_blocks(Bn, H, W, C, F, R, S, stride, brow, 1, nnzb, indptr, indices, values, perm,
+                                     ifmap, ofmap_ref);
 }
 
 }  // extern "C"

@@ -194,6 +194,24 @@ int64_t orc_meta_image(int n_indptr, const int* indptr, int nnzb, const int* ind
     return total;
 }
 
+// brow x bcol blocks as brow x 1 blocks.  Block p of a row block covers the bcol columns
+// indices[p]*bcol + kk, kk = 0..bcol-1, and stores them column by column: value (mm, kk) at
+// values[p*brow*bcol + kk*brow + mm] (block_sparse/spmm/blockwise_format.h:286-297, the same
+// in block_sparse/spconv/blockwise_format.h:71-80).  Both host references add the products
+// of a row in (p, kk) order, which is the order of the expanded column list, so the brow x 1
+// functions below applied to the expanded arrays give the same fp32 sums.  indices1 and
+// values1 hold nnzb*bcol and nnzb*bcol*brow entries.
+void orc_expand_block_columns(int X, int brow, int bcol, const int* indptr, const int* indices,
+                              const uint16_t* values, int* indptr1, int* indices1, uint16_t* values1) {
+    for (int i = 0; i <= X; ++i) indptr1[i] = indptr[i] * bcol;
+    for (int p = 0; p < indptr[X]; ++p)
+        for (int kk = 0; kk < bcol; ++kk) {
+            const size_t q = (size_t)p * bcol + kk;
+            indices1[q] = indices[p] * bcol + kk;
+            for (int mm = 0; mm < brow; ++mm) values1[q * brow + mm] = values[q * brow + mm];
+        }
+}
+
 // fp32 CPU result of D = alpha * (A_sparse . B) + beta * C.
 // Follows block_sparse/spmm/blockwise_format.h:268-311 (bcol == 1): every output
 // element accumulates a*b in ascending non-zero-column order in fp32; the product

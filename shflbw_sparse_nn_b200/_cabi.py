@@ -70,6 +70,7 @@ _PROTOS = {
     "shflbw_matrix_create_random": (C.c_int, [C.c_int] * 4 + [C.c_float, C.c_int, C.c_uint, C.c_int, C.POINTER(_H)]),
     "shflbw_filter_create_random": (C.c_int, [C.c_int] * 6 + [C.c_float, C.c_int, C.c_uint, C.c_int, C.POINTER(_H)]),
     "shflbw_matrix_create_from_arrays": (C.c_int, [C.c_int] * 4 + [C.c_void_p] * 4 + [C.POINTER(_H)]),
+    "shflbw_matrix_create_from_block_arrays": (C.c_int, [C.c_int] * 5 + [C.c_void_p] * 4 + [C.POINTER(_H)]),
     "shflbw_matrix_set_filter_shape": (C.c_int, [_H] + [C.c_int] * 4),
     "shflbw_matrix_load_text": (C.c_int, [C.c_char_p, C.c_size_t, C.POINTER(_H)]),
     "shflbw_matrix_load_file": (C.c_int, [C.c_char_p, C.POINTER(_H)]),

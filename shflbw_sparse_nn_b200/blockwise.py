@@ -91,7 +91,9 @@ class BlockwiseSpMatrix:
         return self
 
     @classmethod
-    def from_arrays(cls, nrow, ncol, brow, indptr, indices, values, row_permute_ids=None):
+    def from_arrays(cls, nrow, ncol, brow, indptr, indices, values, row_permute_ids=None, bcol=1):
+        """Copy caller arrays.  With bcol > 1 the blocks are brow x bcol: `indices` counts in units
+        of bcol columns and `values` holds each block column by column (blockwise_format.h:286-297)."""
         self = cls()
         indptr = np.ascontiguousarray(indptr, dtype=np.int32)
         indices = np.ascontiguousarray(indices, dtype=np.int32)
@@ -100,11 +102,11 @@ class BlockwiseSpMatrix:
         if indptr.size != (nrow // max(brow, 1)) + 1:
             raise ShflbwError(_cabi.ERR_BAD_FORMAT, "from_arrays", "indptr length")
         nnzb = int(indices.size)
-        if values.size != nnzb * brow or (perm is not None and perm.size != nrow):
+        if values.size != nnzb * brow * bcol or (perm is not None and perm.size != nrow):
             raise ShflbwError(_cabi.ERR_BAD_FORMAT, "from_arrays", "array sizes")
         vp = values.ctypes.data if nnzb else None
-        check(_cabi.lib().shflbw_matrix_create_from_arrays(
-            nrow, ncol, brow, nnzb, indptr.ctypes.data, indices.ctypes.data if nnzb else None, vp,
+        check(_cabi.lib().shflbw_matrix_create_from_block_arrays(
+            nrow, ncol, brow, bcol, nnzb, indptr.ctypes.data, indices.ctypes.data if nnzb else None, vp,
             None if perm is None else perm.ctypes.data, C.byref(self._h)), "from_arrays")
         self.initialized = True
         return self
@@ -162,7 +164,7 @@ class BlockwiseSpMatrix:
 
     @property
     def values(self):
-        return self._arr(_cabi.lib().shflbw_matrix_values, self.nnzb * self.brow, np.uint16).view(np.float16)
+        return self._arr(_cabi.lib().shflbw_matrix_values, self.nnzb * self.brow * self.bcol, np.uint16).view(np.float16)
 
     @property
     def row_permute_ids(self):
@@ -189,8 +191,8 @@ class BlockwiseSpFilter(BlockwiseSpMatrix):
         return self
 
     @classmethod
-    def from_arrays(cls, F, R, S, C_, brow, indptr, indices, values, row_permute_ids=None):
-        self = super().from_arrays(F, R * S * C_, brow, indptr, indices, values, row_permute_ids)
+    def from_arrays(cls, F, R, S, C_, brow, indptr, indices, values, row_permute_ids=None, bcol=1):
+        self = super().from_arrays(F, R * S * C_, brow, indptr, indices, values, row_permute_ids, bcol)
         check(_cabi.lib().shflbw_matrix_set_filter_shape(self._h, F, R, S, C_), "set_filter_shape")
         return self
 

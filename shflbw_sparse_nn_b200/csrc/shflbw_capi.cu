@@ -437,7 +437,8 @@ int shflbw_spmm_init(const shflbw_matrix_t* m, int N, const void* B, float alpha
     if (check_kernel_arg(kernel) != SHFLBW_OK) return SHFLBW_ERR_INVALID_ARG;
     if (beta != 0.f && !C) return SHFLBW_ERR_INVALID_ARG;
     if (!on_current_device(*m)) return SHFLBW_ERR_NOT_ON_DEVICE;  // reference: assert(device_synced)
-    if (m->bcol != 1) return SHFLBW_ERR_UNSUPPORTED;            // reference: assert(bcol == BK)
+    // The reference asserts bcol == 1 here (spmm/blockwise_op.h:86); the kernel image lists the
+    // bcol columns of a block one by one, so wider blocks run on the same kernels.
     // Row-block heights 16/32/64/128 (what the reference instantiates, spmm/blockwise_library.cu:15-31)
     // run on the tensor-core kernel.
     if (kernel != SHFLBW_KERNEL_SIMT && m->brow != 16 && m->brow != 32 && m->brow != 64 && m->brow != 128)

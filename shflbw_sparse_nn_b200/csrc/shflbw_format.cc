@@ -77,18 +77,18 @@ uint16_t uniform_half(uint64_t stream, uint64_t index) {
 }
 
 int validate(const shflbw_matrix& m) {
-    if (m.nrow <= 0 || m.ncol <= 0 || m.brow <= 0 || m.bcol != 1) return SHFLBW_ERR_BAD_FORMAT;
-    if (m.nrow % m.brow) return SHFLBW_ERR_BAD_FORMAT;
-    const int X = m.nrow / m.brow;
+    if (m.nrow <= 0 || m.ncol <= 0 || m.brow <= 0 || m.bcol <= 0) return SHFLBW_ERR_BAD_FORMAT;
+    if (m.nrow % m.brow || m.ncol % m.bcol) return SHFLBW_ERR_BAD_FORMAT;
+    const int X = m.nrow / m.brow, Y = m.ncol / m.bcol;
     if ((int)m.indptr.size() != X + 1 || m.indptr[0] != 0 || m.indptr[X] != m.nnzb)
         return SHFLBW_ERR_BAD_FORMAT;
-    if ((int)m.indices.size() != m.nnzb || m.values.size() != (size_t)m.nnzb * m.brow)
+    if ((int)m.indices.size() != m.nnzb || m.values.size() != (size_t)m.nnzb * m.brow * m.bcol)
         return SHFLBW_ERR_BAD_FORMAT;
     for (int i = 0; i < X; ++i) {
         if (m.indptr[i + 1] < m.indptr[i]) return SHFLBW_ERR_BAD_FORMAT;
         for (int p = m.indptr[i]; p < m.indptr[i + 1]; ++p) {
             const int c = m.indices[p];
-            if (c < 0 || c >= m.ncol) return SHFLBW_ERR_BAD_FORMAT;
+            if (c < 0 || c >= Y) return SHFLBW_ERR_BAD_FORMAT;  // block-column units
             if (p > m.indptr[i] && c <= m.indices[p - 1]) return SHFLBW_ERR_BAD_FORMAT;
         }
     }
@@ -137,11 +137,16 @@ void build_host_images(shflbw_matrix& m) {
     // the dense operand) and carries zero values, so it contributes exactly 0.  256 slack
     // rows (zero values, column 0) follow the last block so a full-stage read past the end
     // stays inside the allocation.
+    // A brow x bcol block is bcol adjacent columns that share the row block, and its values
+    // are stored column by column (blockwise_format.h:286-297: a = values[p*brow*bcol +
+    // kk*brow + mm], column indices[p]*bcol + kk).  The image lists those bcol columns one
+    // after the other, so the kernels see the brow x 1 layout whatever bcol is.
+    const size_t bc = (size_t)m.bcol;
     m.kptr.assign(X + 1, 0);
     size_t rows = 0;
     for (int i = 0; i < X; ++i) {
         m.kptr[i] = (int)rows;
-        rows += up((size_t)(m.indptr[i + 1] - m.indptr[i]), kShflbwKPad);
+        rows += up((size_t)(m.indptr[i + 1] - m.indptr[i]) * bc, kShflbwKPad);
     }
     m.kptr[X] = (int)rows;
     const size_t tail = 256;  // slack rows, zero values / index 0
@@ -150,11 +155,14 @@ void build_host_images(shflbw_matrix& m) {
     for (int i = 0; i < X; ++i) {
         const int b = m.indptr[i], e = m.indptr[i + 1];
         size_t r = (size_t)m.kptr[i];
-        for (int p = b; p < e; ++p, ++r) {
-            m.kidx[r] = m.indices[p];
-            for (int j = 0; j < m.brow; ++j) m.kval[kval_index(m.brow, r, j)] = m.values[(size_t)p * m.brow + j];
+        for (int p = b; p < e; ++p) {
+            for (size_t kk = 0; kk < bc; ++kk, ++r) {
+                m.kidx[r] = m.indices[p] * m.bcol + (int)kk;
+                const uint16_t* col = &m.values[((size_t)p * bc + kk) * m.brow];
+                for (int j = 0; j < m.brow; ++j) m.kval[kval_index(m.brow, r, j)] = col[j];
+            }
         }
-        for (; r < (size_t)m.kptr[i + 1]; ++r) m.kidx[r] = e > b ? m.indices[e - 1] : 0;
+        for (; r < (size_t)m.kptr[i + 1]; ++r) m.kidx[r] = e > b ? m.indices[e - 1] * m.bcol + m.bcol - 1 : 0;
     }
     // Filters: the implicit-GEMM gather wants (channel, tap row, tap column) of every column
     // id; decoding once here removes three integer divisions per row from the kernel.
@@ -214,7 +222,7 @@ static void fill_random(shflbw_matrix& m, float requested_density, int value_mod
 static int parse_text(std::istream& in, shflbw_matrix& m) {
     int perm_flag = 0;
     if (!(in >> m.nrow >> m.ncol >> m.nnzb >> m.brow >> m.bcol >> perm_flag)) return SHFLBW_ERR_BAD_FORMAT;
-    if (m.nrow <= 0 || m.ncol <= 0 || m.brow <= 0 || m.bcol != 1 || m.nnzb < 0 || m.nrow % m.brow)
+    if (m.nrow <= 0 || m.ncol <= 0 || m.brow <= 0 || m.bcol <= 0 || m.nnzb < 0 || m.nrow % m.brow || m.ncol % m.bcol)
         return SHFLBW_ERR_BAD_FORMAT;
     m.row_permute = perm_flag != 0;
     m.indptr.resize(m.nrow / m.brow + 1);
@@ -286,8 +294,8 @@ int shflbw_matrix_create_random(int nrow, int ncol, int brow, int bcol, float de
         return SHFLBW_ERR_INVALID_ARG;
     if (value_mode != SHFLBW_VALUES_INT9_LIBC && value_mode != SHFLBW_VALUES_UNIFORM)
         return SHFLBW_ERR_INVALID_ARG;
-    if (bcol != 1) return SHFLBW_ERR_UNSUPPORTED;
-    if (nrow % brow) return SHFLBW_ERR_UNSUPPORTED;  // reference: assert(nrow % brow == 0)
+    // reference: assert(nrow % brow == 0); assert(ncol % bcol == 0)
+    if (nrow % brow || ncol % bcol) return SHFLBW_ERR_UNSUPPORTED;
     auto* m = new (std::nothrow) shflbw_matrix();
     if (!m) return SHFLBW_ERR_INVALID_ARG;
     m->nrow = nrow; m->ncol = ncol; m->brow = brow; m->bcol = bcol;
@@ -316,28 +324,35 @@ int shflbw_matrix_set_filter_shape(shflbw_matrix_t* m, int F, int R, int S, int 
     return SHFLBW_OK;
 }
 
-int shflbw_matrix_create_from_arrays(int nrow, int ncol, int brow, int nnzb, const int* indptr,
-                                     const int* indices, const uint16_t* values, const int* perm,
-                                     shflbw_matrix_t** out) {
+int shflbw_matrix_create_from_block_arrays(int nrow, int ncol, int brow, int bcol, int nnzb, const int* indptr,
+                                           const int* indices, const uint16_t* values, const int* perm,
+                                           shflbw_matrix_t** out) {
     if (!out) return SHFLBW_ERR_INVALID_ARG;
     *out = nullptr;
-    if (nrow <= 0 || ncol <= 0 || brow <= 0 || nnzb < 0 || !indptr || (nnzb > 0 && (!indices || !values)))
+    if (nrow <= 0 || ncol <= 0 || brow <= 0 || bcol <= 0 || nnzb < 0 || !indptr ||
+        (nnzb > 0 && (!indices || !values)))
         return SHFLBW_ERR_INVALID_ARG;
-    if (nrow % brow) return SHFLBW_ERR_UNSUPPORTED;
+    if (nrow % brow || ncol % bcol) return SHFLBW_ERR_UNSUPPORTED;
     auto* m = new (std::nothrow) shflbw_matrix();
     if (!m) return SHFLBW_ERR_INVALID_ARG;
-    m->nrow = nrow; m->ncol = ncol; m->brow = brow; m->bcol = 1; m->nnzb = nnzb;
+    m->nrow = nrow; m->ncol = ncol; m->brow = brow; m->bcol = bcol; m->nnzb = nnzb;
     m->row_permute = perm != nullptr;
     m->indptr.assign(indptr, indptr + nrow / brow + 1);
     m->indices.assign(indices, indices + nnzb);
-    m->values.assign(values, values + (size_t)nnzb * brow);
+    m->values.assign(values, values + (size_t)nnzb * brow * bcol);
     if (perm) m->row_permute_ids.assign(perm, perm + nrow);
-    m->density = (float)nnzb / (nrow / brow) / ncol;
+    m->density = (float)nnzb / (nrow / brow) / (ncol / bcol);
     int rc = validate(*m);
     if (rc != SHFLBW_OK) { delete m; return rc; }
     build_config_str(*m);
     *out = m;
     return SHFLBW_OK;
+}
+
+int shflbw_matrix_create_from_arrays(int nrow, int ncol, int brow, int nnzb, const int* indptr,
+                                     const int* indices, const uint16_t* values, const int* perm,
+                                     shflbw_matrix_t** out) {
+    return shflbw_matrix_create_from_block_arrays(nrow, ncol, brow, 1, nnzb, indptr, indices, values, perm, out);
 }
 
 int shflbw_filter_fold_input_order(const shflbw_matrix_t* f, const shflbw_matrix_t* producer,
@@ -346,6 +361,7 @@ int shflbw_filter_fold_input_order(const shflbw_matrix_t* f, const shflbw_matrix
     *out = nullptr;
     if (!f || !producer || !f->is_filter) return SHFLBW_ERR_INVALID_ARG;
     if (f->C != producer->nrow) return SHFLBW_ERR_BAD_FORMAT;
+    if (f->bcol != 1) return SHFLBW_ERR_UNSUPPORTED;  // a reordered channel list breaks up wider blocks
     // stored position of every logical channel of the producer's output
     std::vector<int> where(f->C);
     for (int p = 0; p < f->C; ++p) where[producer->row_permute ? producer->row_permute_ids[p] : p] = p;

@@ -136,9 +136,11 @@ class ShflBWConv2d(nn.Module):
 def densify(m) -> np.ndarray:
     """Logical dense matrix (rows in original order) of a Shfl-BW object, fp16."""
     d = np.zeros((m.nrow, m.ncol), np.float16)
-    v = np.asarray(m.values).view(np.float16).reshape(-1, m.brow)
+    v = np.asarray(m.values).view(np.float16).reshape(-1, m.brow)   # one row per stored column
     perm = m.row_permute_ids if m.row_permute else np.arange(m.nrow)
-    indptr, indices = m.indptr, m.indices
+    bcol = m.bcol
+    indptr = m.indptr * bcol
+    indices = (m.indices[:, None] * bcol + np.arange(bcol)[None, :]).reshape(-1)
     for i in range(m.nrow // m.brow):
         rows = perm[i * m.brow:(i + 1) * m.brow]
         cols = indices[indptr[i]:indptr[i + 1]]

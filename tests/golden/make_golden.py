@@ -12,6 +12,8 @@ Writes:
                           reference builder for a grid of (shape, V, density, permute, seed)
   spmm_cases.npz          reference get_host_reference outputs (fp32) on small seeded inputs
   spconv_cases.npz        reference conv get_host_reference outputs (fp32), reference layouts
+  block_column_cases.npz  the same three kinds of output for brow x bcol blocks with bcol > 1
+                          (`python tests/golden/make_golden.py blocks` writes this file alone)
 """
 from __future__ import annotations
 
@@ -49,8 +51,65 @@ BUILDER_GRID = [
 ]
 
 
+def write_block_column_cases() -> None:
+    """bcol > 1: the reference's builder and both of its host references."""
+    z = {}
+    grid = [  # nrow, ncol, brow, bcol, density, permute, seed
+        (256, 256, 32, 2, 0.1, True, 2021),
+        (512, 384, 64, 4, 0.2, False, 5),
+        (128, 1024, 16, 8, 0.15, True, 9),
+    ]
+    for i, (nrow, ncol, brow, bcol, d, perm, seed) in enumerate(grid):
+        r = oa.RefMatrix.init_random(nrow, ncol, brow, d, perm, seed, bcol=bcol)
+        z[f"b{i}_args"] = np.array([nrow, ncol, brow, bcol, int(perm), seed, r.nnzb], np.int64)
+        z[f"b{i}_density_req"], z[f"b{i}_density"] = np.float32(d), np.float32(r.density)
+        z[f"b{i}_indptr"], z[f"b{i}_indices"] = r.indptr, r.indices
+        if perm:
+            z[f"b{i}_perm"] = r.perm
+        z[f"b{i}_config_str"] = np.frombuffer(r.config_str.encode(), np.uint8)
+    z["n_builder"] = np.int64(len(grid))
+    cases = [  # M, K, N, V, bcol, density, permute, seed, beta
+        (128, 256, 40, 32, 2, 0.2, True, 11, 0.0),
+        (256, 192, 64, 64, 4, 0.25, True, 12, 1.0),
+        (64, 128, 24, 16, 8, 0.3, False, 13, 0.0),
+    ]
+    for i, (M, K, N, V, bcol, d, perm, seed, beta) in enumerate(cases):
+        r = oa.RefMatrix.init_random(M, K, V, d, perm, seed, bcol=bcol)
+        vals = uniform_half(seed, r.nnzb * V * bcol)
+        B = uniform_half(seed + 1000, K * N).reshape(K, N)
+        Cm = uniform_half(seed + 2000, M * N).reshape(M, N) if beta != 0.0 else None
+        D = oa.ref_spmm_host_reference(M, K, N, V, r.indptr, r.indices, vals, r.perm, B, 1.0, Cm, beta, bcol=bcol)
+        z[f"s{i}_args"] = np.array([M, K, N, V, bcol, int(perm), seed], np.int64)
+        z[f"s{i}_beta"] = np.float32(beta)
+        z[f"s{i}_indptr"], z[f"s{i}_indices"] = r.indptr, r.indices
+        if perm:
+            z[f"s{i}_perm"] = r.perm
+        z[f"s{i}_D"] = D
+    z["n_spmm"] = np.int64(len(cases))
+    ccases = [  # B, H, W, C, F, R, S, stride, V, bcol, density, permute, seed
+        (8, 6, 6, 16, 64, 3, 3, 1, 32, 2, 0.2, True, 21),
+        (8, 5, 7, 24, 128, 3, 3, 1, 64, 4, 0.3, False, 22),   # C % bcol == 0, blocks stay inside a tap
+        (8, 4, 4, 9, 64, 1, 1, 1, 32, 3, 0.5, True, 23),
+    ]
+    for i, (Bn, H, W, Cc, F, R, S, st, V, bcol, d, perm, seed) in enumerate(ccases):
+        r = oa.RefMatrix.filter_init_random(F, R, S, Cc, V, d, perm, seed, bcol=bcol)
+        vals = uniform_half(seed, r.nnzb * V * bcol)
+        x = uniform_half(seed + 1000, Cc * H * W * Bn).reshape(Cc, H, W, Bn)
+        O = oa.ref_spconv_host_reference(Bn, H, W, Cc, F, R, S, st, V, r.indptr, r.indices, vals, r.perm, x, bcol=bcol)
+        z[f"v{i}_args"] = np.array([Bn, H, W, Cc, F, R, S, st, V, bcol, int(perm), seed], np.int64)
+        z[f"v{i}_indptr"], z[f"v{i}_indices"] = r.indptr, r.indices
+        if perm:
+            z[f"v{i}_perm"] = r.perm
+        z[f"v{i}_O"] = O
+    z["n_spconv"] = np.int64(len(ccases))
+    np.savez_compressed(HERE / "block_column_cases.npz", **z)
+
+
 def main() -> None:
     assert oa.ref_host() is not None, "build oracle/_ref first (make -C oracle)"
+    if sys.argv[1:] == ["blocks"]:
+        write_block_column_cases()
+        return
     # -- 1. the reference's own golden file --------------------------------------------
     gold = REF_GOLDEN.read_bytes()
     m = oa.RefMatrix.init_random(1024, 1024, 32, 0.2, False, 2021)  # first rand() consumer here
@@ -131,6 +190,7 @@ def main() -> None:
         cv[f"v{i}_O"] = O
     cv["n_cases"] = np.int64(len(ccases))
     np.savez_compressed(HERE / "spconv_cases.npz", **cv)
+    write_block_column_cases()
     print("golden fixtures written to", HERE)
 
 

@@ -44,6 +44,7 @@ def orc() -> C.CDLL:
         l.orc_spmm_ref.argtypes = [C.c_int] * 3 + [C.c_void_p] * 5 + [C.c_float, C.c_void_p, C.c_float, C.c_void_p, C.c_int]
         l.orc_spconv_ref_chwn.argtypes = [C.c_int] * 9 + [C.c_void_p] * 6 + [C.c_int]
         l.orc_spconv_ref_nhwc.argtypes = [C.c_int] * 9 + [C.c_void_p] * 5 + [C.c_float, C.c_void_p, C.c_int]
+        l.orc_expand_block_columns.argtypes = [C.c_int] * 3 + [C.c_void_p] * 6
         l.orc_check_equal_ref_rule.restype = C.c_int64
         l.orc_check_equal_ref_rule.argtypes = [C.c_int64, C.c_void_p, C.c_void_p]
         _orc = l
@@ -78,21 +79,31 @@ def srand(seed=1):
     orc().orc_srand(seed)
 
 
-def dump_text(nrow, ncol, brow, indptr, indices, values, perm):
+def dump_text(nrow, ncol, brow, indptr, indices, values, perm, bcol=1):
     nnzb = int(indices.size)
     v = np.ascontiguousarray(values).view(np.uint16)
-    args = (nrow, ncol, nnzb, brow, 1, 0 if perm is None else 1, _P(indptr), _P(indices), _P(v), _P(perm))
+    args = (nrow, ncol, nnzb, brow, bcol, 0 if perm is None else 1, _P(indptr), _P(indices), _P(v), _P(perm))
     n = orc().orc_dump_text(*args, None, 0)
     buf = C.create_string_buffer(n)
     orc().orc_dump_text(*args, C.cast(buf, C.c_void_p), n)
     return buf.raw
 
 
-def meta_image(indptr, indices, perm):
+def meta_image(indptr, indices, perm, bcol=1):
     n_perm = 0 if perm is None else int(perm.size)
     out = np.zeros(indptr.size + indices.size + n_perm + 32, np.int32)
-    n = orc().orc_meta_image(int(indptr.size), _P(indptr), int(indices.size), _P(indices), 1, n_perm, _P(perm), _P(out))
+    n = orc().orc_meta_image(int(indptr.size), _P(indptr), int(indices.size), _P(indices), bcol, n_perm, _P(perm), _P(out))
     return out[:n].copy()
+
+
+def expand_block_columns(brow, bcol, indptr, indices, values):
+    """brow x bcol blocks as brow x 1 blocks: (indptr, indices, values) for the other functions here."""
+    indptr = np.ascontiguousarray(indptr, np.int32)
+    indices = np.ascontiguousarray(indices, np.int32)
+    v = np.ascontiguousarray(values).view(np.uint16)
+    ip1, ix1, v1 = np.zeros_like(indptr), np.zeros(indices.size * bcol, np.int32), np.zeros_like(v)
+    orc().orc_expand_block_columns(indptr.size - 1, brow, bcol, _P(indptr), _P(indices), _P(v), _P(ip1), _P(ix1), _P(v1))
+    return ip1, ix1, v1.view(np.float16)
 
 
 def spmm_ref(M, N, brow, indptr, indices, values, perm, B, alpha=1.0, Cm=None, beta=0.0, threads=8):
@@ -157,6 +168,8 @@ def ref_host():
         l.ref_matrix_meta_image.argtypes = [C.c_void_p, C.c_void_p, C.c_int64]
         l.ref_spmm_host_reference.argtypes = [C.c_int] * 5 + [C.c_void_p] * 5 + [C.c_float, C.c_void_p, C.c_float, C.c_void_p]
         l.ref_spconv_host_reference.argtypes = [C.c_int] * 10 + [C.c_void_p] * 6
+        l.ref_spmm_host_reference_blocks.argtypes = [C.c_int] * 6 + [C.c_void_p] * 5 + [C.c_float, C.c_void_p, C.c_float, C.c_void_p]
+        l.ref_spconv_host_reference_blocks.argtypes = [C.c_int] * 11 + [C.c_void_p] * 6
         _ref_host = l
     return _ref_host
 
@@ -164,14 +177,14 @@ def ref_host():
 class RefMatrix:
     """A BlockwiseSpMatrix<half> / BlockwiseSpFilter<half> built by the reference itself."""
 
-    def __init__(self, handle, nrow, brow, permute):
-        self.h, self.nrow, self.brow, self.permute = handle, nrow, brow, permute
+    def __init__(self, handle, nrow, brow, permute, bcol=1):
+        self.h, self.nrow, self.brow, self.permute, self.bcol = handle, nrow, brow, permute, bcol
         l = ref_host()
         self.nnzb = l.ref_matrix_nnzb(handle)
         self.density = l.ref_matrix_density(handle)
         self.indptr = np.zeros(nrow // brow + 1, np.int32)
         self.indices = np.zeros(self.nnzb, np.int32)
-        v = np.zeros(self.nnzb * brow, np.uint16)
+        v = np.zeros(self.nnzb * brow * bcol, np.uint16)
         self.perm = np.zeros(nrow, np.int32) if permute else None
         l.ref_matrix_arrays(handle, _P(self.indptr), _P(self.indices), _P(v), _P(self.perm))
         self.values = v.view(np.float16)
@@ -180,12 +193,12 @@ class RefMatrix:
         self.config_str = buf.value.decode()
 
     @classmethod
-    def init_random(cls, nrow, ncol, brow, density, permute, seed):
-        return cls(ref_host().ref_matrix_init_random(nrow, ncol, brow, 1, density, int(permute), seed), nrow, brow, permute)
+    def init_random(cls, nrow, ncol, brow, density, permute, seed, bcol=1):
+        return cls(ref_host().ref_matrix_init_random(nrow, ncol, brow, bcol, density, int(permute), seed), nrow, brow, permute, bcol)
 
     @classmethod
-    def filter_init_random(cls, F, R, S, Cc, brow, density, permute, seed):
-        return cls(ref_host().ref_filter_init_random(F, R, S, Cc, brow, 1, density, int(permute), seed), F, brow, permute)
+    def filter_init_random(cls, F, R, S, Cc, brow, density, permute, seed, bcol=1):
+        return cls(ref_host().ref_filter_init_random(F, R, S, Cc, brow, bcol, density, int(permute), seed), F, brow, permute, bcol)
 
     def dump(self):
         l = ref_host()
@@ -207,22 +220,22 @@ class RefMatrix:
             pass
 
 
-def ref_spmm_host_reference(M, K, N, brow, indptr, indices, values, perm, B, alpha=1.0, Cm=None, beta=0.0):
+def ref_spmm_host_reference(M, K, N, brow, indptr, indices, values, perm, B, alpha=1.0, Cm=None, beta=0.0, bcol=1):
     D = np.zeros((M, N), np.float32)
     v = np.ascontiguousarray(values).view(np.uint16)
     b = np.ascontiguousarray(B).view(np.uint16)
     c = None if Cm is None else np.ascontiguousarray(Cm).view(np.uint16)
-    ref_host().ref_spmm_host_reference(M, K, N, brow, int(indices.size), _P(indptr), _P(indices), _P(v), _P(perm),
-                                       _P(b), alpha, _P(c), beta, _P(D))
+    ref_host().ref_spmm_host_reference_blocks(M, K, N, brow, bcol, int(indices.size), _P(indptr), _P(indices), _P(v),
+                                              _P(perm), _P(b), alpha, _P(c), beta, _P(D))
     return D
 
 
-def ref_spconv_host_reference(Bn, H, W, Cc, F, R, S, stride, brow, indptr, indices, values, perm, ifmap_chwn):
+def ref_spconv_host_reference(Bn, H, W, Cc, F, R, S, stride, brow, indptr, indices, values, perm, ifmap_chwn, bcol=1):
     out = np.zeros((F, H, W, Bn), np.float32)
     v = np.ascontiguousarray(values).view(np.uint16)
     x = np.ascontiguousarray(ifmap_chwn).view(np.uint16)
-    ref_host().ref_spconv_host_reference(Bn, H, W, Cc, F, R, S, stride, brow, int(indices.size), _P(indptr),
-                                         _P(indices), _P(v), _P(perm), _P(x), _P(out))
+    ref_host().ref_spconv_host_reference_blocks(Bn, H, W, Cc, F, R, S, stride, brow, bcol, int(indices.size),
+                                                _P(indptr), _P(indices), _P(v), _P(perm), _P(x), _P(out))
     return out
 
 

@@ -101,7 +101,7 @@ def test_malformed_inputs_are_rejected_not_aborted():
     with pytest.raises(sb.ShflbwError):
         sb.BlockwiseSpMatrix().init_random(100, 64, 32, 1, 0.1, False, 1)   # nrow % brow != 0
     with pytest.raises(sb.ShflbwError):
-        sb.BlockwiseSpMatrix().init_random(64, 64, 32, 2, 0.1, False, 1)    # bcol != 1
+        sb.BlockwiseSpMatrix().init_random(64, 63, 32, 2, 0.1, False, 1)    # ncol % bcol != 0
     with pytest.raises(sb.ShflbwError):
         sb.BlockwiseSpMatrix().load(b"4 4 2 2 1 0 0 1")                     # truncated text
     sb.BlockwiseSpMatrix.from_arrays(4, 8, 2, ok_ptr, ok_idx, vals, None)   # the good one passes
