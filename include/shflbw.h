@@ -170,7 +170,7 @@ typedef struct shflbw_spmm_state {
     int tokens_per_cta;      /* dense-dimension tile of one work item */
     int stages;              /* shared-memory pipeline depth */
     int producer_warps;      /* warps issuing the gather */
-    int variant;             /* 0: tokens in TMEM lanes; 1: rows of the block in TMEM lanes */
+    int variant;             /* 0: tokens in TMEM lanes; 1: rows of the block in TMEM lanes; 2: as 0 with 16 epilogue warps */
     int num_items, tiles_n;  /* work items = row blocks x dense tiles */
     unsigned grid_x, grid_y, block_x;
     size_t shared_mem_size;
@@ -231,7 +231,8 @@ typedef struct shflbw_spconv_state {
     int tokens_per_cta;
     int stages;
     int producer_warps;
-    int variant;             /* 0: tokens in TMEM lanes; 1: filters in TMEM lanes (NHWC calls: planes out + transpose) */
+    int variant;             /* 0: tokens in TMEM lanes; 1: filters in TMEM lanes (NHWC calls: planes out + transpose);
+                                2: as 0 with 16 epilogue warps (chained layers) */
     int num_items, tiles_n;
     unsigned grid_x, grid_y, block_x;
     size_t shared_mem_size;

@@ -116,24 +116,34 @@ constexpr int kPanelSpmm = 0, kPanelConv = 1, kPanelConvChain = 2, kPanelSpmmRow
 //                   step; row ids travel in registers (loaded two stages ahead).
 constexpr int kGatherCpAsync = 0, kGatherTma = 1, kGatherCpAsyncArrive = 2;
 
-template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1, int GATHER_ = kGatherCpAsync>
+// EW: epilogue warps, 8 or 16.  A warp can read only the TMEM lane quadrant warp % 4, so the
+// warps of a quadrant split the accumulator columns between them.  Items with few non-zero
+// columns are all epilogue, and one warp's chain (TMEM read, convert, transpose, store) is
+// latency-bound: sixteen warps keep four such chains per scheduler in flight instead of two.
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1, int GATHER_ = kGatherCpAsync,
+          int EW_ = 8>
 struct PanelCfg {
+    static constexpr int EW = EW_;
+    static_assert(EW == 8 || EW == 16, "epilogue warps");
     static constexpr bool TMA = GATHER_ == kGatherTma;
     static constexpr bool ARRIVE = GATHER_ == kGatherCpAsyncArrive;
     static constexpr int KS = KS_;                         // non-zero columns per pipeline stage
     static constexpr int T = 128 * TM;
     static constexpr int GROUPS = GROUPS_;                 // producer groups that take the stages in turn
     static constexpr int LAG = LAG_;                       // a group publishes a stage while issuing its LAG-th next one
-    // Warp w runs on scheduler partition w % 4.  The MMA warp (8) sits on partition 0 and no
-    // producer shares it: warps 12, 16, 20... of the block stay idle.  The MMA warp executes a
+    // Warp w runs on scheduler partition w % 4.  The MMA warp (the first after the epilogue
+    // warps: 8 or 16) sits on partition 0 and no producer shares it: the later warps with
+    // w % 4 == 0 stay idle.  The MMA warp executes a
     // few dozen instructions per stage and was measured at ~20 clk per instruction when
     // producer code kept evicting its lines from the partition's instruction cache.
-    static constexpr int WARPS_USED = 9 + PW + (PW - 1) / 3;   // 8 epilogue + MMA + producers + idle
+    static constexpr int WARPS_USED = EW + 1 + PW + (PW - 1) / 3;   // epilogue + MMA + producers + idle
     // Register budgets per role.  Up to 20 warps every thread can have the ~100 registers the
     // epilogue wants.  Beyond that the block is padded to whole warpgroups (4 warps) and
     // launched at 65536 / threads registers per thread; the producer / MMA warpgroups then give
     // registers back (setmaxnreg.dec) and the two epilogue warpgroups take them (setmaxnreg.inc).
-    static constexpr bool REG_SPLIT = WARPS_USED > 20;
+    // (With 16 epilogue warps the block is 20 warps at 96 registers and is not split.)
+    static constexpr bool REG_SPLIT = EW == 8 && WARPS_USED > 20;
+    static_assert(EW == 8 || WARPS_USED <= 20, "16 epilogue warps: at most 3 producers (20 warps leave 96 registers per thread, 21-24 only 80)");
     static constexpr int WARPS = REG_SPLIT ? (WARPS_USED + 3) / 4 * 4 : WARPS_USED;
     static constexpr int THREADS = WARPS * 32;
     static constexpr int REGS_LEAN = 56;                                    // producers, MMA warp, idle warps
@@ -156,8 +166,8 @@ struct PanelCfg {
     // Epilogue tiles (tokens in lanes only): each epilogue warp transposes 32 tokens x 32 output
     // rows / filters through 2 KB so that its global stores are 16 bytes per lane and 64-byte
     // runs.  With rows in lanes the stores go straight from registers.
-    static constexpr int OUT_BYTES = (MODE == kPanelSpmmRows || MODE == kPanelConvChainRows) ? 0 : 8 * 2048;
-    static constexpr int BAR_BYTES = (STAGES * 2 + 8) * 8;   // mbarriers + tmem slot + abort flag
+    static constexpr int OUT_BYTES = (MODE == kPanelSpmmRows || MODE == kPanelConvChainRows) ? 0 : EW * 2048;
+    static constexpr int BAR_BYTES = (STAGES * 2 + 12) * 8;  // mbarriers (ring, up to 4 + 4 accumulator, drain) + tmem slot + abort flag
     static constexpr int TAB_BYTES = 512 * 8;               // per-CTA item table (kPanelMaxItemsPerCta entries)
     static constexpr int IDX_AHEAD = LAG + 1;              // a group fetches row ids this many of its stages ahead
     static constexpr int IDX_RING = (IDX_AHEAD + 1) * GROUPS <= 8 ? 8 : 16;   // stages of row ids kept in shared memory
@@ -168,7 +178,12 @@ struct PanelCfg {
     static constexpr int KG_BYTES = SWAP ? T * 16 : 2048;   // 8 gathered rows (one K group) of the token tile
     static constexpr uint32_t ACC_COLS = SWAP ? T : TM * V; // fp32 columns of one accumulator set
     static_assert(!SWAP || V == 64 || V == 128, "rows-in-lanes needs a legal UMMA M");
-    static constexpr uint32_t TMEM_COLS = 2 * ACC_COLS < 32 ? 32 : 2 * ACC_COLS;  // double buffered
+    // Accumulator sets in TMEM: two (the MMAs of item i+1 run while the epilogue reads item i);
+    // four with sixteen epilogue warps, whose items are so short that the hand-over itself
+    // (commit -> barrier -> poll -> TMEM read -> release -> poll -> issue) is what two sets
+    // cannot hide.
+    static constexpr int NBUF = (EW == 16 && ACC_COLS * 4 <= 512) ? 4 : 2;
+    static constexpr uint32_t TMEM_COLS = NBUF * ACC_COLS < 32 ? 32 : NBUF * ACC_COLS;
     static_assert(V == 16 || V == 32 || V == 64 || V == 128, "row-block height");
     static_assert(V != 16 || (TM == 1 && !SWAP), "16-row blocks: tokens in lanes, one 128-token accumulator");
     static_assert(!TMA || (MODE == kPanelSpmmRows && V == 64), "TMA gather: SpMM with rows in lanes, 64-row blocks");
@@ -196,14 +211,17 @@ __device__ __forceinline__ uint32_t tile32_off(int r, int c) { return (uint32_t)
 
 constexpr int kPanelMaxItemsPerCta = 512;  // capacity of the per-CTA item table
 
-template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1, int GATHER_ = kGatherCpAsync>
-__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_, GATHER_>::THREADS, 1)
+template <int V, int TM, int KS_, int STAGES, int PW, int MODE, int GROUPS_ = 2, int LAG_ = 1, int GATHER_ = kGatherCpAsync,
+          int EW_ = 8>
+__global__ void __launch_bounds__(PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_, GATHER_, EW_>::THREADS, 1)
 panel_umma_kernel(const __grid_constant__ PanelParams p) {
-    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_, GATHER_>;
+    using Cfg = PanelCfg<V, TM, KS_, STAGES, PW, MODE, GROUPS_, LAG_, GATHER_, EW_>;
+    constexpr int EW = Cfg::EW;                                             // epilogue warps 0..EW-1, MMA warp EW, producers after it
     constexpr bool SWAP = Cfg::SWAP;                                        // rows in TMEM lanes
     constexpr bool CONV = MODE == kPanelConv || MODE == kPanelConvChain || MODE == kPanelConvChainRows;  // implicit-GEMM gather
     constexpr bool CHAIN = MODE == kPanelConvChain || MODE == kPanelConvChainRows;
     constexpr bool ROWS_OUT = MODE == kPanelSpmm || MODE == kPanelConvChain; // transposing epilogue: rows out, tokens contiguous
+    static_assert(EW == 8 || (ROWS_OUT && Cfg::ACC_COLS >= 128), "16 epilogue warps: transposing epilogue, >= 32 columns per warp");
     constexpr int KS = Cfg::KS, T = Cfg::T;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: swizzle atoms are addressed by absolute shared-memory address bits.
@@ -211,11 +229,12 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
     uint8_t* bar_area = smem + Cfg::PIPE_BYTES + Cfg::OUT_BYTES;
     uint64_t* full_bar = (uint64_t*)bar_area;          // [STAGES] producers -> MMA
     uint64_t* empty_bar = full_bar + STAGES;           // [STAGES] MMA -> producers
-    uint64_t* acc_full = empty_bar + STAGES;           // [2] MMA -> epilogue
-    uint64_t* acc_empty = acc_full + 2;                // [2] epilogue -> MMA
-    uint32_t* tmem_slot = (uint32_t*)(acc_empty + 2);
+    constexpr int NBUF = Cfg::NBUF;
+    uint64_t* acc_full = empty_bar + STAGES;           // [NBUF] MMA -> epilogue
+    uint64_t* acc_empty = acc_full + NBUF;             // [NBUF] epilogue -> MMA
+    uint32_t* tmem_slot = (uint32_t*)(acc_empty + NBUF);
     volatile int* cta_abort = (volatile int*)(tmem_slot + 1);
-    uint64_t* drain_bar = acc_empty + 3;               // abort path only: MMA thread waits for its last MMAs
+    uint64_t* drain_bar = acc_empty + NBUF + 1;        // abort path only: MMA thread waits for its last MMAs
     int2* item_tab = (int2*)(bar_area + Cfg::BAR_BYTES);  // [nloc] (first padded row, padded row count)
     int* idx_ring = (int*)(bar_area + Cfg::BAR_BYTES + Cfg::TAB_BYTES);  // [IDX_RING][KS] row ids of upcoming stages
 
@@ -248,9 +267,9 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             sm100::mbar_init(&full_bar[s], Cfg::TMA ? 1 : Cfg::ARRIVE ? (PW / Cfg::GROUPS) * 32 : PW / Cfg::GROUPS);
             sm100::mbar_init(&empty_bar[s], 1);   // one tcgen05.commit per drain
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NBUF; ++b) {
             sm100::mbar_init(&acc_full[b], 1);
-            sm100::mbar_init(&acc_empty[b], 8);   // one arrival per epilogue warp
+            sm100::mbar_init(&acc_empty[b], EW);  // one arrival per epilogue warp
         }
         sm100::mbar_init(drain_bar, 1);
         *cta_abort = 0;
@@ -261,7 +280,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         const int b0 = __ldg(p.blk_ptr + blk);
         item_tab[li] = make_int2(b0, __ldg(p.blk_ptr + blk + 1) - b0);
     }
-    if (warp == 8) {
+    if (warp == EW) {
         sm100::tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
         sm100::tmem_relinquish();
     }
@@ -279,16 +298,16 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
     if (tid == 0) TRACE(3, 0, 0);
     if (tid == 0) CTRACE(1);
 
-    const int pidx = warp - 9 - (warp / 4 - 2);   // producer number of a producer warp (warps 9.. with warp % 4 != 0)
+    const int pidx = warp - (EW + 1) - (warp / 4 - EW / 4);   // producer number of a producer warp (warps after the MMA warp with warp % 4 != 0)
     if constexpr (Cfg::REG_SPLIT) {
         // Whole warpgroups change their register budget together: warps 0-7 (epilogue) grow,
         // every other warpgroup (MMA warp, producers, idle and padding warps) shrinks first.
-        if (warp < 8) sm100::setmaxnreg_inc<Cfg::REGS_EPI>();
+        if (warp < EW) sm100::setmaxnreg_inc<Cfg::REGS_EPI>();
         else sm100::setmaxnreg_dec<Cfg::REGS_LEAN>();
     }
-    if (warp >= 9 && ((warp & 3) == 0 || pidx >= PW)) {
+    if (warp > EW && ((warp & 3) == 0 || pidx >= PW)) {
         // idle: keeps producers off the MMA warp's scheduler partition (or pads the last warpgroup)
-    } else if (warp >= 9 && Cfg::TMA) {
+    } else if (warp > EW && Cfg::TMA) {
         // ---------------------------------------------------- producers (TMA gather) ----
         // A stage is KS gathered rows x T tokens = (KS/4) row quads x (T/64) column boxes, one
         // tile::gather4 each (4 rows x 128 bytes, landing as half a swizzle atom).  The GW warps
@@ -385,7 +404,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         }
 #endif
         }
-    } else if (warp >= 9 && Cfg::ARRIVE) {
+    } else if (warp > EW && Cfg::ARRIVE) {
         // ------------------------------------- producers (cp.async, deferred arrivals) ----
         // The GW warps of a group share a stage (RPW rows each); a warp instruction copies RPI
         // rows of the token tile, 16 bytes per lane, straight into the swizzled layout.  After its
@@ -516,7 +535,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         }
 #endif
         }
-    } else if (warp >= 9) {
+    } else if (warp > EW) {
         // ------------------------------------------------------------- producers ----
         // The PW producer warps form GROUPS groups that take the CTA's stages in turn (group g
         // fills stages g, g+GROUPS, ...).  While one group sits in its barrier round trip
@@ -726,7 +745,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             o[0] = pc_empty; o[1] = pc_n; o[2] = clock64() - pc_t0;
         }
 #endif
-    } else if (warp == 8) {
+    } else if (warp == EW) {
         // ------------------------------------------------------------ MMA warp ----
         constexpr uint32_t idesc = SWAP ? sm100::make_idesc_f16_mnmajor(V, T) : sm100::make_idesc_f16_mnmajor(128, V);
         // Descriptors are built once; per MMA only the 16-byte-granular start address field
@@ -755,11 +774,11 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             for (int li = 0; li < nloc; ++li) {
                 const int rows_total = item_tab[li].y;
                 const int num_k = (rows_total + KS - 1) / KS;
-                const int b = li & 1;
+                const int b = li % NBUF;
 #ifdef SHFLBW_COUNTERS
                 const long long a0c = clock64();
 #endif
-                if (li >= 2 && !sm100::mbar_wait_bounded(&acc_empty[b], ((li >> 1) - 1) & 1, cta_abort, p.status_word,
+                if (li >= NBUF && !sm100::mbar_wait_bounded(&acc_empty[b], ((li / NBUF) - 1) & 1, cta_abort, p.status_word,
                                                          SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 20))
                     break;                                   // timed out or aborted: issue nothing more
 #ifdef SHFLBW_COUNTERS
@@ -850,10 +869,11 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         if (lane == 0) CTRACE(3);
     } else {
         // -------------------------------------------------------------- epilogue ----
-        // Eight warps: warp w reads TMEM lane quadrant w % 4 (tokens) and half w / 4 of the
-        // accumulator columns (the block's output rows / filters).
+        // Warp w reads TMEM lane quadrant w % 4 (tokens) and part w / 4 of the accumulator
+        // columns (the block's output rows / filters): halves with eight warps, quarters with
+        // sixteen.
         const int quad = warp & 3, half_id = warp >> 2;
-        constexpr int HALVES = Cfg::ACC_COLS >= 64 ? 2 : 1;   // a 16- or 32-column accumulator is not split
+        constexpr int HALVES = Cfg::ACC_COLS >= 64 ? EW / 4 : 1;   // a 16- or 32-column accumulator is not split
         constexpr int COLS = Cfg::ACC_COLS / HALVES;          // fp32 columns handled by this warp
         constexpr int CW = COLS < 32 ? COLS : 32;             // columns per pass through the 2 KB tile
         const bool reads = half_id < HALVES;
@@ -870,13 +890,13 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const int blk = item / p.tiles_n;
             const int n0 = (item % p.tiles_n) * T;
             const bool has_k = item_tab[li].y > 0 && !(ablate & 1);
-            const int b = li & 1;
+            const int b = li % NBUF;
             // Wait for the item's accumulator (one lane polls, the warp follows).  false: the wait
             // timed out or the block is aborting -- store nothing more.
             auto wait_accumulator = [&]() -> bool {
                 int acc_ok = 1;
                 if (lane == 0)
-                    acc_ok = sm100::mbar_wait_bounded(&acc_full[b], (li >> 1) & 1, cta_abort, p.status_word,
+                    acc_ok = sm100::mbar_wait_bounded(&acc_full[b], (li / NBUF) & 1, cta_abort, p.status_word,
                                                       SHFLBW_DEVSTAT_TIMEOUT_ACCUM, p.wait_limit, 32);
                 if (!__shfl_sync(0xffffffffu, acc_ok, 0)) return false;
                 sm100::tc_fence_after_sync();
@@ -1044,60 +1064,75 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             // SpMM: thread = token, accumulator columns = the block's output rows.  For a fixed
             // row a warp's 32 tokens are only 64 contiguous bytes of D, and storing them straight
             // from registers is one 2-byte-per-lane store per row.  Instead each chunk of 32 rows
-            // goes through a [32 rows][32 tokens] tile in shared memory (2-byte writes, one row =
-            // 64 contiguous bytes, conflict-free) and comes back as 16-byte pieces: four lanes
-            // store one row's 64 bytes, eight rows per store instruction.  The inverse row
-            // permutation is the row index of those stores.
-            __half* my_tile = (__half*)(smem + Cfg::PIPE_BYTES + warp * 2048);
+            // goes through a tile in shared memory as 16 row PAIRS x 32 tokens of half2 (one
+            // packed conversion, one multiply and one 4-byte conflict-free write per pair) and
+            // comes back as 16-byte pieces: a lane reads 8 tokens of a pair (two 16-byte reads,
+            // the 16-byte units of odd pairs swapped so that a quarter warp covers all banks),
+            // splits them into the pair's two rows with byte permutes and stores 16 bytes of
+            // each; four lanes store one row's 64 bytes, eight rows per store instruction.  The
+            // inverse row permutation is the row index of those stores.
+            uint32_t* my_tile = (uint32_t*)(smem + Cfg::PIPE_BYTES + warp * 2048);
             const int tg = lane & 3;                                    // 8-token group stored by this lane
-            const int tok_g = reads ? n0 + a0 * 128 + quad * 32 + tg * 8 : p.N;
-            const bool ok_g = tok_g < p.N && !(ablate & 8);             // N % 8 == 0: a group is valid as a whole
-            // Element offset of the group inside an output row.  SpMM: the token index.  Chained
-            // SpConv: 8 images of one output pixel inside the next layer's halo-padded plane
-            // (images beyond the batch are computed from zero inputs and are written as zeros).
-            uint32_t goff = (uint32_t)tok_g;
-            __half* const obase = MODE == kPanelSpmm ? p.D : p.out;
-            if constexpr (MODE == kPanelConvChain) {
-                if (ok_g) {
-                    const int pix = tok_g / p.Bp, nn = tok_g - pix * p.Bp;
-                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
-                    goff = (uint32_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
+            // Slot j = 2i + h of a chunk is row 16i + 2*(lane/4) + h: pair 8i + lane/4, half h.
+            auto slot_row = [&](int j) { return 16 * (j >> 1) + 2 * (lane >> 2) + (j & 1); };
+            constexpr int NSLOT = CW / 8;                               // rows stored per lane and chunk
+            // This lane's 8-token group of an item whose tile starts at token n0_: is it inside N
+            // (N % 8 == 0: a group is valid as a whole), and its element offset inside an output
+            // row.  SpMM: the token index.  Chained SpConv: 8 images of one output pixel inside the
+            // next layer's halo-padded plane (images beyond the batch are computed from zero inputs
+            // and are written as zeros).
+            auto group_offset = [&](int n0_, bool& ok_) -> uint32_t {
+                const int tok_g = reads ? n0_ + a0 * 128 + quad * 32 + tg * 8 : p.N;
+                ok_ = tok_g < p.N && !(ablate & 8);
+                uint32_t goff_ = (uint32_t)tok_g;
+                if constexpr (MODE == kPanelConvChain) {
+                    if (ok_) {
+                        const int pix = tok_g / p.Bp, nn = tok_g - pix * p.Bp;
+                        const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                        goff_ = (uint32_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
+                    }
                 }
-            }
+                return goff_;
+            };
+            bool ok_g;
+            const uint32_t goff = group_offset(n0, ok_g);
+            __half* const obase = MODE == kPanelSpmm ? p.D : p.out;
             const __half2 zero2 = __float2half2_rn(0.f);
             // What gets added to the product (beta * C, or the residual of a chained layer) does not
             // depend on the accumulator: the addends of the item's first two chunks are requested
             // BEFORE waiting for it, each later chunk's two chunks ahead, so that their global-memory
-            // latency is off the critical path (these layers are often all epilogue).
+            // latency is off the critical path (these layers are often all epilogue).  (Requesting
+            // the NEXT item's addend a whole item ahead was measured 3-5 % slower on the residual
+            // layers of the ResNet stack, which run at ~4.1 TB/s of HBM traffic either way.)
             constexpr int NCH = COLS / CW;
             const bool add_res = MODE == kPanelConvChain && p.res != nullptr;
             const bool need_add = ok_g && (use_c || add_res);
-            uint4 addend[2][4];
-            auto fetch_addend = [&](int cc, uint4 (&dst)[4]) {
+            uint4 addend[NCH > 1 ? 2 : 1][4];
+            auto fetch_addend = [&](int blk_, uint32_t goff_, int cc, uint4 (&dst)[4]) {
 #pragma unroll
-                for (int i = 0; i < CW / 8; ++i) {
-                    const int m = mbase + cc + 8 * i + (lane >> 2);
+                for (int i = 0; i < NSLOT; ++i) {
+                    const int m = mbase + cc + slot_row(i);
                     if (use_c) {
-                        const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
-                        dst[i] = *(const uint4*)(p.C + (size_t)((uint32_t)row * (uint32_t)p.N) + (size_t)goff);
+                        const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk_ * V + m) : blk_ * V + m;
+                        dst[i] = *(const uint4*)(p.C + (size_t)((uint32_t)row * (uint32_t)p.N) + (size_t)goff_);
                     } else {
-                        const uint32_t rr = (uint32_t)(p.res_map ? __ldg(p.res_map + blk * V + m) : blk * V + m) * (uint32_t)p.out_plane;
-                        dst[i] = *(const uint4*)(p.res + (size_t)rr + (size_t)goff);
+                        const uint32_t rr = (uint32_t)(p.res_map ? __ldg(p.res_map + blk_ * V + m) : blk_ * V + m) * (uint32_t)p.out_plane;
+                        dst[i] = *(const uint4*)(p.res + (size_t)rr + (size_t)goff_);
                     }
                 }
             };
             if (need_add) {
-                fetch_addend(0, addend[0]);
-                if constexpr (NCH > 1) fetch_addend(CW, addend[1]);
+                fetch_addend(blk, goff, 0, addend[0]);
+                if constexpr (NCH > 1) fetch_addend(blk, goff, CW, addend[1]);
             }
             if (!wait_accumulator()) break;
 #pragma unroll
             for (int ch = 0; ch < NCH; ++ch) {
                 const int cc = ch * CW;
-                uint32_t roff[4];                                        // D offsets of rows cc + 8i + lane/4
+                uint32_t roff[4];                                        // D offsets of this lane's rows
 #pragma unroll
-                for (int i = 0; i < CW / 8; ++i) {
-                    const int m = mbase + cc + 8 * i + (lane >> 2);
+                for (int i = 0; i < NSLOT; ++i) {
+                    const int m = mbase + cc + slot_row(i);
                     if constexpr (MODE == kPanelSpmm) {
                         const int row = (p.perm && !(ablate & 1024)) ? __ldg(p.perm + blk * V + m) : blk * V + m;
                         roff[i] = (uint32_t)row * (uint32_t)p.N;
@@ -1125,29 +1160,38 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                     // Same epilogue arithmetic as the reference: round to fp16, then alpha (and
                     // beta * C, applied after the transpose) in fp16.
 #pragma unroll
-                    for (int e = 0; e < CW; ++e) {
-                        __half h = __float2half_rn(__uint_as_float(r[e]));
-                        if (!use_c) h = __hmul(h, alpha1);
-                        my_tile[e * 32 + lane] = h;
+                    for (int q = 0; q < CW / 2; ++q) {
+                        __half2 h = __floats2half2_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1]));
+                        if (!use_c) h = __hmul2(h, alpha2);
+                        my_tile[q * 32 + (lane ^ ((q & 1) << 2))] = *(uint32_t*)&h;
                     }
                 }
                 __syncwarp();
                 if (!(ablate & 512)) {
 #pragma unroll
-                    for (int i = 0; i < CW / 8; ++i) {
-                        uint4 v = *(const uint4*)(my_tile + (8 * i + (lane >> 2)) * 32 + tg * 8);
+                    for (int k = 0; k < NSLOT / 2; ++k) {
+                        const int q = 8 * k + (lane >> 2);   // 8 tokens of this lane's k-th row pair
+                        const uint32_t* src = my_tile + q * 32;
+                        const uint4 w0 = *(const uint4*)(src + (((2 * tg) ^ (q & 1)) << 2));
+                        const uint4 w1 = *(const uint4*)(src + (((2 * tg + 1) ^ (q & 1)) << 2));
+#pragma unroll
+                    for (int i = 2 * k; i < 2 * k + 2; ++i) {
+                        const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;   // the pair's second / first row
+                        uint4 v;
+                        v.x = __byte_perm(w0.x, w0.y, sel); v.y = __byte_perm(w0.z, w0.w, sel);
+                        v.z = __byte_perm(w1.x, w1.y, sel); v.w = __byte_perm(w1.z, w1.w, sel);
                         if (ok_g) {
                             const size_t off = (size_t)roff[i] + (size_t)goff;
                             if (use_c) {
                                 __half* h = (__half*)&v;
-                                const __half* cadd = (const __half*)&addend[ch & 1][i];
+                                const __half* cadd = (const __half*)&addend[NCH > 1 ? (ch & 1) : 0][i];
 #pragma unroll
                                 for (int e = 0; e < 8; ++e) h[e] = __hfma(h[e], alpha1, __hmul(cadd[e], beta1));
                             }
                             if constexpr (MODE == kPanelConvChain) {   // out = relu(alpha * conv + residual), fp16
                                 __half2* h = (__half2*)&v;
                                 if (add_res) {
-                                    const __half2* rh = (const __half2*)&addend[ch & 1][i];
+                                    const __half2* rh = (const __half2*)&addend[NCH > 1 ? (ch & 1) : 0][i];
 #pragma unroll
                                     for (int e = 0; e < 4; ++e) h[e] = __hadd2(h[e], rh[e]);
                                 }
@@ -1159,8 +1203,9 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                             *(uint4*)(obase + off) = v;
                         }
                     }
+                    }
                 }
-                if (need_add && ch + 2 < NCH) fetch_addend(cc + 2 * CW, addend[ch & 1]);
+                if constexpr (NCH > 2) { if (need_add && ch + 2 < NCH) fetch_addend(blk, goff, cc + 2 * CW, addend[ch & 1]); }
                 __syncwarp();
             }
             } else {
@@ -1211,7 +1256,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             if (tid == 0) TRACE(2, li, 3);
         }
 #ifdef SHFLBW_COUNTERS
-        if (lane == 0 && p.trace != nullptr) {   // per epilogue warp: cycles waiting for an accumulator, cycles in the role
+        if (lane == 0 && p.trace != nullptr && warp < 8) {   // per epilogue warp: cycles waiting for an accumulator, cycles in the role
             unsigned long long* o = p.trace + 148 * 48 + (blockIdx.x * 8 + warp) * 2;
             o[0] = ec_wait; o[1] = clock64() - ec_t0;
         }
@@ -1231,7 +1276,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
     __syncthreads();
     if (tid == 0) TRACE(3, 0, 1);
     if (tid == 0) CTRACE(5);
-    if (warp == 8) {
+    if (warp == EW) {
         sm100::tc_fence_after_sync();
         sm100::tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
     }

@@ -108,10 +108,11 @@ int host_pipeline(shflbw_matrix* m, cudaStream_t* s_in, cudaStream_t* s_k, cudaS
 using PanelKernel = void (*)(const shflbw::PanelParams);
 struct PanelChoice { PanelKernel fn; size_t smem; int tokens; int stages; int pw; int threads; int variant; int gather; };
 
-template <int V, int TM, int KS, int STAGES, int PW, int MODE, int GROUPS = 2, int LAG = 1, int GATHER = shflbw::kGatherCpAsync>
+template <int V, int TM, int KS, int STAGES, int PW, int MODE, int GROUPS = 2, int LAG = 1, int GATHER = shflbw::kGatherCpAsync,
+          int EW = 8>
 PanelChoice choice() {
-    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG, GATHER>;
-    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG, GATHER>, (size_t)Cfg::SMEM_BYTES, Cfg::T,
+    using Cfg = shflbw::PanelCfg<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG, GATHER, EW>;
+    return {shflbw::panel_umma_kernel<V, TM, KS, STAGES, PW, MODE, GROUPS, LAG, GATHER, EW>, (size_t)Cfg::SMEM_BYTES, Cfg::T,
             STAGES, PW, Cfg::THREADS, 0, GATHER};
 }
 
@@ -193,7 +194,17 @@ bool tuned_shape(PanelChoice* out) {
 // Pipeline shape per (V, tile): non-zero columns per stage (KS) and ring depth (as many stages
 // as fit beside the 16 KB of epilogue tiles).
 template <int MODE>
-bool lookup(int V, int tile, PanelChoice* out, int gather = shflbw::kGatherCpAsync) {
+bool lookup(int V, int tile, PanelChoice* out, int gather = shflbw::kGatherCpAsync, bool wide_epilogue = false) {
+    if constexpr (MODE == shflbw::kPanelSpmm || MODE == shflbw::kPanelConvChain) {
+        // Shallow items (at most 64 non-zero columns): sixteen epilogue warps and three producer
+        // warps, each a group of its own (20 warps: 96 registers per thread); stages of 32 columns,
+        // eight of them beside the 32 KB of epilogue tiles, so that up to eight items' inputs are
+        // in flight from HBM.  Built for 64-row blocks.
+        if (wide_epilogue && tile == 256 && V == 64) {
+            *out = choice<64, 2, 32, 8, 3, MODE, 3, 1, shflbw::kGatherCpAsync, 16>();
+            return true;
+        }
+    }
     if constexpr (MODE == shflbw::kPanelSpmmRows || MODE == shflbw::kPanelConvChainRows) {   // rows in TMEM lanes: V must be a legal UMMA M
 #ifdef SHFLBW_TUNE
         if (V == 64 && tile == 256 && tuned_shape<MODE>(out)) return true;
@@ -301,8 +312,17 @@ int pick_panel(int V, long long n_tokens, int row_blocks, long long padded_cols,
                                                  : lookup<shflbw::kPanelConvChainRows>(V, tile, out);
         }
     }
-    if (!swapped && !lookup<MODE>(V, tile, out)) return SHFLBW_ERR_UNSUPPORTED;
-    out->variant = swapped ? 1 : 0;
+    // Tokens in lanes with at most one stage of non-zero columns per block on average (an item is
+    // then all epilogue; with two stages the four producers of that kernel were measured slower
+    // than the eight of the regular one) and several items per SM: sixteen epilogue warps.  SHFLBW_EPILOGUE_WARPS=8|16 forces the choice
+    // (tuning aid).
+    bool wide = false;
+    if constexpr (MODE == shflbw::kPanelSpmm || MODE == shflbw::kPanelConvChain) {
+        wide = !swapped && tile == 256 && V == 64 && padded_cols <= 64ll * row_blocks && items256 >= 4ll * sms;
+        if (const char* e = getenv("SHFLBW_EPILOGUE_WARPS")) wide = !swapped && tile == 256 && V == 64 && atoi(e) == 16;
+    }
+    if (!swapped && !lookup<MODE>(V, tile, out, shflbw::kGatherCpAsync, wide)) return SHFLBW_ERR_UNSUPPORTED;
+    out->variant = swapped ? 1 : wide ? 2 : 0;
     return allow_smem(out->fn, out->smem);
 }
 
@@ -492,7 +512,7 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         // recorded configuration (the shared-memory attribute was set at init).
         PanelChoice ch;
         const bool found = st->variant == 1 ? lookup<shflbw::kPanelSpmmRows>(st->V, st->tokens_per_cta, &ch, st->gather)
-                                            : lookup<shflbw::kPanelSpmm>(st->V, st->tokens_per_cta, &ch);
+                                            : lookup<shflbw::kPanelSpmm>(st->V, st->tokens_per_cta, &ch, shflbw::kGatherCpAsync, st->variant == 2);
         if (!found) return SHFLBW_ERR_INVALID_ARG;
         shflbw::PanelParams p{};
         p.blk_ptr = st->blk_ptr; p.blk_idx = st->blk_idx; p.blk_val = (const __half*)st->blk_val;
@@ -733,7 +753,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     PanelChoice ch;
     const bool ok_kernel = (!st->chain && !planes) ? lookup<shflbw::kPanelConv>(st->V, st->tokens_per_cta, &ch)
                            : st->variant == 1      ? lookup<shflbw::kPanelConvChainRows>(st->V, st->tokens_per_cta, &ch)
-                                                   : lookup<shflbw::kPanelConvChain>(st->V, st->tokens_per_cta, &ch);
+                                                   : lookup<shflbw::kPanelConvChain>(st->V, st->tokens_per_cta, &ch, shflbw::kGatherCpAsync, st->variant == 2);
     if (!ok_kernel) return SHFLBW_ERR_INVALID_ARG;
     // 1. NHWC -> channel-major, batch-innermost staging with a zero halo (chained layers get
     //    their input in that layout already).
@@ -762,7 +782,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     p.Bn = st->B; p.Bp = st->Bp; p.Hp = Hp; p.Wp = Wp; p.Cin = st->C; p.F = st->F;
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
     p.num_items = st->num_items; p.tiles_n = st->tiles_n;
-#ifdef SHFLBW_ABLATE
+#if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
     if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
     if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
 #endif

@@ -54,6 +54,24 @@ def operand_swap(mode):
             os.environ["SHFLBW_SWAP"] = old
 
 
+@contextmanager
+def epilogue_warps(n):
+    """Force the 8- or 16-epilogue-warp kernels (tokens in lanes, 64-row blocks, 256-token tile)
+    for ops initialised inside the block; None leaves the library's own choice."""
+    old = os.environ.get("SHFLBW_EPILOGUE_WARPS")
+    if n is None:
+        os.environ.pop("SHFLBW_EPILOGUE_WARPS", None)
+    else:
+        os.environ["SHFLBW_EPILOGUE_WARPS"] = str(int(n))
+    try:
+        yield
+    finally:
+        if old is None:
+            os.environ.pop("SHFLBW_EPILOGUE_WARPS", None)
+        else:
+            os.environ["SHFLBW_EPILOGUE_WARPS"] = old
+
+
 def run_spmm(m, N, B, alpha=1.0, Cm=None, beta=0.0, kernel=sb.KERNEL_AUTO, tokens=None, poison=True):
     """D = alpha*A.B + beta*C on the GPU through SpmmBlockwiseOp; returns D as numpy fp16."""
     m.transform_and_sync_device()

@@ -10,7 +10,7 @@ import torch
 import oracle_api as oa
 import shflbw_sparse_nn_b200 as sb
 from conftest import assert_close_fp16
-from gpu_util import dev, host, operand_swap, run_spconv
+from gpu_util import dev, epilogue_warps, host, operand_swap, run_spconv, tile
 
 pytestmark = pytest.mark.gpu
 
@@ -76,7 +76,7 @@ def test_two_chained_layers_match_oracle_and_unchained_path(stride2):
     assert_close_fp16(got, y2_unchained.astype(np.float32), what="chained vs unchained GPU path")
 
 
-@pytest.mark.parametrize("swap", [0, 1])
+@pytest.mark.parametrize("swap", [0, 1, 2])
 def test_residual_add_across_two_chained_layers(swap):
     """y = relu(conv2(relu(conv1(x))) + x): an identity shortcut around two chained layers.  x is
     imported in logical channel order, conv2's output is in conv2's stored filter order, so the
@@ -101,9 +101,11 @@ def test_residual_add_across_two_chained_layers(swap):
     b2 = _chain_buf(Cc, H, W, Bn, 1, 1)
     y = torch.full((Bn, H, W, Cc), float("nan"), dtype=torch.float16, device="cuda")
     sb.chain_import_nhwc(dev(x), Bn, H, W, Cc, 1, 1, b0, s)
-    with operand_swap(swap):
+    # swap 2: tokens in lanes with sixteen epilogue warps (the kernel the library picks for shallow layers with many items)
+    with operand_swap(1 if swap == 1 else 0), epilogue_warps(16 if swap == 2 else 8), tile(256 if swap == 2 else None):
         l1 = sb.SpconvChainOp().initialize(f1, Bn, H, W, 1, b0, b1, 3, 3, alpha=0.25, relu=True)
         l2 = sb.SpconvChainOp().initialize(f2c, Bn, H, W, 1, b1, b2, 1, 1, alpha=0.25, relu=True)
+    assert l1._state.variant == swap and l2._state.variant == swap
     l2.set_residual(b0, residual_producer=None)    # b0 holds logical channel order
     l1(s); l2(s)
     sb.chain_export_nhwc(b2, Bn, H, W, Cc, 1, 1, f2c, y, s)

@@ -13,7 +13,7 @@ import torch
 import oracle_api as oa
 import shflbw_sparse_nn_b200 as sb
 from conftest import assert_close_fp16
-from gpu_util import dev, host, operand_swap, run_spmm
+from gpu_util import dev, epilogue_warps, host, operand_swap, run_spmm
 
 pytestmark = pytest.mark.gpu
 
@@ -228,6 +228,37 @@ def test_both_operand_orientations(V, swap, tokens):
     assert op._state.variant == swap and op2._state.variant == swap
     assert_close_fp16(D, _oracle(m, N, B, 0.5, Cm, -1.5), what=f"V={V} swap={swap} alpha/beta")
     assert_close_fp16(D2, _oracle(m, N, B), what=f"V={V} swap={swap}")
+
+
+@pytest.mark.parametrize("density,N", [(0.05, 1000), (0.09, 4096), (0.35, 520)])
+def test_sixteen_epilogue_warp_kernel(density, N):
+    """Tokens in lanes with sixteen epilogue warps (four accumulator sets, 32-column stages, three
+    producer groups): picked by the library for shallow blocks with many items, forced here also
+    on deeper ones (several stages per item).  alpha, beta * C, permutation, ragged dense width,
+    empty blocks."""
+    M, K, V = 512, 640, 64
+    m = sb.BlockwiseSpMatrix().init_random(M, K, V, 1, density, True, 31, values="uniform")
+    B = sb.uniform_half(32, K * N).reshape(K, N)
+    Cm = sb.uniform_half(33, M * N).reshape(M, N)
+    with operand_swap(0), epilogue_warps(16):
+        D, op = run_spmm(m, N, B, alpha=0.5, Cm=Cm, beta=-1.5, tokens=256)
+        D2, op2 = run_spmm(m, N, B, tokens=256)
+    assert op._state.variant == 2 and op2._state.variant == 2 and op._state.producer_warps == 3
+    assert_close_fp16(D, _oracle(m, N, B, 0.5, Cm, -1.5), what="16 epilogue warps, alpha/beta")
+    assert_close_fp16(D2, _oracle(m, N, B), what="16 epilogue warps")
+    with operand_swap(0), epilogue_warps(8):
+        D3, op3 = run_spmm(m, N, B, tokens=256)
+    assert op3._state.variant == 0
+    assert np.array_equal(D2.view(np.uint16), D3.view(np.uint16))    # same arithmetic, same order
+
+
+def test_library_picks_sixteen_epilogue_warps_for_shallow_blocks_with_many_items():
+    m = sb.BlockwiseSpMatrix().init_random(256, 256, 64, 1, 0.2, True, 5, values="uniform")   # ~51 columns per block
+    N = 256 * 148
+    B = sb.uniform_half(6, 256 * N).reshape(256, N)
+    D, op = run_spmm(m, N, B)
+    assert op._state.variant == 2
+    assert_close_fp16(D, _oracle(m, N, B), what="auto 16 epilogue warps")
 
 
 @pytest.mark.parametrize("N", [8, 40, 136])
