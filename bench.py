@@ -170,11 +170,20 @@ class Dist:
 
 def capture_steps(torch, launch, steps, stream, use_graph=True):
     """Capture G consecutive steps (G = largest divisor of `steps` up to 200) into a CUDA graph.
-    Returns (run, G): run() executes exactly `steps` steps on `stream`; G == 0 means plain launches.
-    launch(i, raw_stream) enqueues step i."""
+    Returns (run, G, est): run() executes exactly `steps` steps on `stream`; G == 0 means plain
+    launches; est = measured ms per step of a short untimed run (one graph replay, or up to 200 plain
+    launches -- not the whole block, so that the timed region is not preceded by a run as long as
+    itself).  launch(i, raw_stream) enqueues step i."""
     G = max((g for g in range(1, min(steps, 200) + 1) if steps % g == 0), default=0) if use_graph else 0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if G < 2:
-        return (lambda: [launch(i, stream.cuda_stream) for i in range(steps)]), 0
+        n = min(steps, 200)
+        e0.record(stream)
+        for i in range(n):
+            launch(i, stream.cuda_stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return (lambda: [launch(i, stream.cuda_stream) for i in range(steps)]), 0, e0.elapsed_time(e1) / n
     side = torch.cuda.Stream()
     side.wait_stream(stream)
     with torch.cuda.stream(side):
@@ -186,7 +195,11 @@ def capture_steps(torch, launch, steps, stream, use_graph=True):
     torch.cuda.synchronize()
     graph.replay()                          # one untimed replay (graph upload)
     torch.cuda.synchronize()
-    return (lambda: [graph.replay() for _ in range(steps // G)]), G
+    e0.record(stream)
+    graph.replay()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return (lambda: [graph.replay() for _ in range(steps // G)]), G, e0.elapsed_time(e1) / G
 
 
 def timed_blocks(torch, dist, run_block, steps, est_ms_per_step, stream):
@@ -268,13 +281,7 @@ def run_ours(args):
 
     # The timed loop is launch-gap sensitive (a kernel of a few tens of microseconds per step):
     # consecutive steps are captured once into a CUDA graph and the graph is replayed.
-    run_steps, G = capture_steps(torch, launch, args.steps, stream, use_graph=not args.no_graph)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    run_steps()                                  # untimed: sizes the number of blocks
-    e1.record(stream)
-    torch.cuda.synchronize()
-    est = e0.elapsed_time(e1) / args.steps
+    run_steps, G, est = capture_steps(torch, launch, args.steps, stream, use_graph=not args.no_graph)
     ms_step, ms_lo, ms_hi, R, t_wall0, t_wall1 = timed_blocks(torch, dist, run_steps, args.steps, est, stream)
     m.device_status()
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
@@ -306,7 +313,9 @@ def run_ours(args):
                    "nnzb": nnzb, "batches_rotated": NB, "l2": "inputs larger than L2 (4 x 67 MB rotated)",
                    "per_gpu": "one 4096-column batch per step on every GPU; sparse operand replicated",
                    "timing": f"{R} blocks of {args.steps} steps, median block (max over ranks) / steps",
-                   "launch": (f"CUDA graph of {G} steps replayed {args.steps // G}x per block" if G else "one host launch per step")},
+                   "launch": (f"CUDA graph of {G} steps replayed {args.steps // G}x per block" if G else "one host launch per step"),
+                   "power": ("a timed region of ~60 ms runs at the full SM clock; 100+ ms of back-to-back launches of this "
+                             "kernel reach the board's power cap (sw_power_cap, ~1.85-1.89 GHz measured: ~36.7 us per step)")},
         "dense_equivalent_tflops": round(world * flops_dense / (ms_step * 1e-3) / 1e12, 2),
         "roofline": roofline, "gpu_launches": R * args.steps * ops[0].launches_per_exec, "clocks": clocks,
     }
@@ -406,14 +415,8 @@ def bench_spconv(sb, torch, dist, pk, steps=300, warmup=20, use_graph=True):
         ops[i % NBc](stream)
     torch.cuda.synchronize()
     lib = _cabi.lib()
-    run_steps, G = capture_steps(torch, lambda i, raw: lib.shflbw_spconv_exec(C.byref(ops[i % NBc]._state), raw), steps,
+    run_steps, G, est = capture_steps(torch, lambda i, raw: lib.shflbw_spconv_exec(C.byref(ops[i % NBc]._state), raw), steps,
                                  stream, use_graph=use_graph)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record(stream)
-    run_steps()
-    e1.record(stream)
-    torch.cuda.synchronize()
-    est = e0.elapsed_time(e1) / steps
     ms, lo, hi, R, _, _ = timed_blocks(torch, dist, run_steps, steps, est, stream)
     f.device_status()
     t = ms * 1e-3
@@ -633,7 +636,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every timed step from the host instead of replaying a CUDA graph")
