@@ -56,6 +56,28 @@ namespace shflbw {
 
 constexpr long long kWaitLimitCycles = 400000000LL;   // default bound of every in-kernel wait: ~0.2 s at 2 GHz
 
+// Division of a non-negative int below 2^31 by a divisor fixed per launch: the quotient is
+// umulhi(n, mul) >> shr with mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1
+// (d == 1: the number itself).  Four instructions instead of the ~25 of a 32-bit division in
+// software; the epilogues of shallow items are instruction-bound and divide three times per item.
+struct FastDiv {
+    unsigned d, mul, shr;
+};
+inline FastDiv make_fast_div(int d) {
+    FastDiv f{(unsigned)d, 0u, 0u};
+    if (d > 1) {
+        unsigned c = 0;
+        while ((1ull << c) < (unsigned long long)d) ++c;         // ceil(log2 d)
+        const unsigned p = 31 + c;
+        f.mul = (unsigned)(((1ull << p) + (unsigned long long)d - 1) / (unsigned long long)d);
+        f.shr = p - 32;
+    }
+    return f;
+}
+__device__ __forceinline__ int fast_div(int n, const FastDiv& f) {
+    return f.d == 1u ? n : (int)(__umulhi((unsigned)n, f.mul) >> f.shr);
+}
+
 struct alignas(64) PanelParams {
     // TMA gather only: tensor map of B ([K][N] fp16, box = 64 tokens x 1 row, 128-byte swizzle); first
     // member so that it sits on the 64-byte boundary the copy engine wants
@@ -72,6 +94,7 @@ struct alignas(64) PanelParams {
     long long wait_limit;    // SM clocks after which a barrier wait gives up (kWaitLimitCycles unless the host overrides it)
     float alpha, beta;
     int num_items, tiles_n;  // work items = row blocks x token tiles; item -> (item / tiles_n, item % tiles_n)
+    FastDiv div_tiles, div_bp, div_wo;   // division by tiles_n, Bp, Wo (set by the host with make_fast_div)
     unsigned long long* trace;  // tuning builds only: per-role timestamps of CTA 0
     int inject_from;         // fault-injection builds only (-DSHFLBW_FAULT_INJECT): from this stage number on, one
                              // producer warp withholds its arrivals, so the consumer's bounded wait runs out (< 0: off)
@@ -276,7 +299,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         sm100::mbar_init_fence();
     }
     for (int li = tid; li < nloc; li += blockDim.x) {
-        const int blk = ((int)blockIdx.x + li * (int)gridDim.x) / p.tiles_n;
+        const int blk = fast_div((int)blockIdx.x + li * (int)gridDim.x, p.div_tiles);
         const int b0 = __ldg(p.blk_ptr + blk);
         item_tab[li] = make_int2(b0, __ldg(p.blk_ptr + blk + 1) - b0);
     }
@@ -358,7 +381,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const int num_k = (ent.y + KS - 1) / KS;
             if (num_k == 0) continue;
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int col = (item % p.tiles_n) * T + cbox * 64;     // first token of this lane's box (beyond N: zero fill)
+            const int col = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T + cbox * 64;     // first token of this lane's box (beyond N: zero fill)
             const __half* wsrc = p.blk_val + (size_t)ent.x * V;
             for (int kt = 0; kt < num_k; ++kt, ++it) {
                 if ((it % GROUPS) != grp) continue;
@@ -468,14 +491,14 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const int num_k = (ent.y + KS - 1) / KS;
             if (num_k == 0) continue;
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int tok0 = (item % p.tiles_n) * T + chunk * 8;
+            const int tok0 = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T + chunk * 8;
             const bool chunk_ok = tok0 < p.N;
             const uint32_t nbytes = chunk_ok ? 16u : 0u;
             const __half* conv_src0 = p.Xs;
             if constexpr (CONV) {
                 if (chunk_ok) {
-                    const int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
-                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                    const int pix = fast_div(tok0, p.div_bp), nn = tok0 - pix * p.Bp;
+                    const int oh = fast_div(pix, p.div_wo), ow = pix - oh * p.Wo;
                     conv_src0 = p.Xs + ((oh * p.stride * p.Wp + ow * p.stride) * p.Bp + nn);
                 }
             }
@@ -622,7 +645,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             if (num_k == 0) continue;
             // per-item decode of this lane's tokens
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int tok0 = (item % p.tiles_n) * T + chunk * 8;
+            const int tok0 = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T + chunk * 8;
             const bool chunk_ok = tok0 < p.N;
             const uint32_t nbytes = chunk_ok ? 16u : 0u;
             // SpConv: this lane's 8 tokens are 8 images of one output pixel; the staged input
@@ -630,8 +653,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const __half* conv_src0 = p.Xs;
             if constexpr (CONV) {
                 if (chunk_ok) {
-                    const int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
-                    const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                    const int pix = fast_div(tok0, p.div_bp), nn = tok0 - pix * p.Bp;
+                    const int oh = fast_div(pix, p.div_wo), ow = pix - oh * p.Wo;
                     conv_src0 = p.Xs + ((oh * p.stride * p.Wp + ow * p.stride) * p.Bp + nn);
                 }
             }
@@ -887,8 +910,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const long long ew0 = clock64();
 #endif
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int blk = item / p.tiles_n;
-            const int n0 = (item % p.tiles_n) * T;
+            const int blk = fast_div(item, p.div_tiles);
+            const int n0 = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T;
             const bool has_k = item_tab[li].y > 0 && !(ablate & 1);
             const int b = li % NBUF;
             // Wait for the item's accumulator (one lane polls, the warp follows).  false: the wait
@@ -950,8 +973,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                         if constexpr (CHAIN) {
                             // 8 consecutive tokens are 8 images of one output pixel; the pixel's place in the
                             // consumer's halo-padded plane is found once and stepped from group to group
-                            int pix = tok0 / p.Bp, nn = tok0 - pix * p.Bp;
-                            int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                            int pix = fast_div(tok0, p.div_bp), nn = tok0 - pix * p.Bp;
+                            int oh = fast_div(pix, p.div_wo), ow = pix - oh * p.Wo;
 #pragma unroll
                             for (int c = 0; c < 4; ++c) {
                                 goffs[c] = (size_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
@@ -1050,9 +1073,9 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             bool ok = tok < p.N && !(ablate & 8);
             uint32_t row_off[4];                           // SpConv: output offsets of positions i*8 + lane/4
             if constexpr (MODE == kPanelConv) {
-                const int pix = tok / p.Bp, img = tok - pix * p.Bp;
+                const int pix = fast_div(tok, p.div_bp), img = tok - pix * p.Bp;
                 ok = ok && img < p.Bn;
-                const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                const int oh = fast_div(pix, p.div_wo), ow = pix - oh * p.Wo;
                 // this position's F-vector at the block's filters (element offset; host checks it fits 32 bits)
                 const uint32_t mine = ok ? (uint32_t)((img * p.Ho + oh) * p.Wo + ow) * (uint32_t)p.F + (uint32_t)(blk * V + mbase)
                                          : 0xffffffffu;
@@ -1087,8 +1110,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
                 uint32_t goff_ = (uint32_t)tok_g;
                 if constexpr (MODE == kPanelConvChain) {
                     if (ok_) {
-                        const int pix = tok_g / p.Bp, nn = tok_g - pix * p.Bp;
-                        const int oh = pix / p.Wo, ow = pix - oh * p.Wo;
+                        const int pix = fast_div(tok_g, p.div_bp), nn = tok_g - pix * p.Bp;
+                        const int oh = fast_div(pix, p.div_wo), ow = pix - oh * p.Wo;
                         goff_ = (uint32_t)(((oh + p.oph) * p.OWp + ow + p.opw) * p.Bp + nn);
                     }
                 }

@@ -523,6 +523,7 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         if (ch.gather != st->gather) return SHFLBW_ERR_INVALID_ARG;
         if (st->gather == shflbw::kGatherTma) std::memcpy(p.tmap_b, st->tmap_b, sizeof p.tmap_b);
         p.num_items = st->num_items; p.tiles_n = st->tiles_n;
+        p.div_tiles = shflbw::make_fast_div(st->tiles_n); p.div_bp = p.div_wo = shflbw::make_fast_div(1);
 #if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
         if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
         if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
@@ -782,6 +783,7 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     p.Bn = st->B; p.Bp = st->Bp; p.Hp = Hp; p.Wp = Wp; p.Cin = st->C; p.F = st->F;
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
     p.num_items = st->num_items; p.tiles_n = st->tiles_n;
+    p.div_tiles = shflbw::make_fast_div(st->tiles_n); p.div_bp = shflbw::make_fast_div(st->Bp); p.div_wo = shflbw::make_fast_div(st->Wo);
 #if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
     if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
     if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
