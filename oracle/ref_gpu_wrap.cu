@@ -35,6 +35,7 @@ struct ConvCfg { int V; const char* name; SpconvBlockwiseInitFn_t init; SpconvBl
 
 // A subset of the tile list of block_sparse/spmm/blockwise_library.cu (names as there).
 const SpmmCfg kSpmm[] = {
+    CFG(16, 64, 32, 16, 16, 32, 4),  CFG(16, 128, 32, 16, 32, 32, 4), CFG(16, 256, 32, 16, 64, 32, 4),
     CFG(32, 64, 32, 32, 16, 32, 4),  CFG(32, 128, 32, 32, 32, 32, 4), CFG(32, 256, 32, 32, 64, 32, 3),
     CFG(64, 64, 32, 32, 32, 32, 4),  CFG(64, 128, 32, 32, 32, 32, 4), CFG(64, 128, 32, 64, 32, 32, 3),
     CFG(64, 256, 16, 32, 64, 16, 3),

@@ -208,7 +208,7 @@ struct PanelCfg {
     static constexpr int NBUF = (EW == 16 && ACC_COLS * 4 <= 512) ? 4 : 2;
     static constexpr uint32_t TMEM_COLS = NBUF * ACC_COLS < 32 ? 32 : NBUF * ACC_COLS;
     static_assert(V == 16 || V == 32 || V == 64 || V == 128, "row-block height");
-    static_assert(V != 16 || (TM == 1 && !SWAP), "16-row blocks: tokens in lanes, one 128-token accumulator");
+    static_assert(V != 16 || !SWAP, "16-row blocks: tokens in lanes");
     static_assert(!TMA || (MODE == kPanelSpmmRows && V == 64), "TMA gather: SpMM with rows in lanes, 64-row blocks");
     static_assert(STAGE_BYTES % 1024 == 0, "stages must keep 1024-byte swizzle-atom alignment");
     static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns");
@@ -896,7 +896,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         // columns (the block's output rows / filters): halves with eight warps, quarters with
         // sixteen.
         const int quad = warp & 3, half_id = warp >> 2;
-        constexpr int HALVES = Cfg::ACC_COLS >= 64 ? EW / 4 : 1;   // a 16- or 32-column accumulator is not split
+        // (a single 16- or 32-column accumulator is not split; two 16-column accumulators go to the two halves)
+        constexpr int HALVES = (Cfg::ACC_COLS >= 64 || (V == 16 && TM == 2)) ? EW / 4 : 1;
         constexpr int COLS = Cfg::ACC_COLS / HALVES;          // fp32 columns handled by this warp
         constexpr int CW = COLS < 32 ? COLS : 32;             // columns per pass through the 2 KB tile
         const bool reads = half_id < HALVES;

@@ -227,8 +227,9 @@ bool lookup(int V, int tile, PanelChoice* out, int gather = shflbw::kGatherCpAsy
         }
     } else {
         if constexpr (MODE == shflbw::kPanelSpmm || MODE == shflbw::kPanelConv) {
-            // 16-row blocks: UMMA N = 16, one 128-token accumulator per item (18 KB stages)
+            // 16-row blocks: UMMA N = 16, one or two 128-token accumulators per item (18 / 34 KB stages)
             if (V == 16 && tile == 128) { *out = choice<16, 1, 64, 8, 8, MODE>(); return true; }
+            if (V == 16 && tile == 256) { *out = choice<16, 2, 64, 5, 8, MODE>(); return true; }
         }
         switch (V * 1000 + tile) {
             case 32128:  *out = choice<32, 1, 64, 8, 8, MODE>(); return true;    // 20 KB stages
@@ -291,7 +292,9 @@ int pick_panel(int V, long long n_tokens, int row_blocks, long long padded_cols,
     const long long waves256 = (items256 + sms - 1) / sms, waves128 = (items128 + sms - 1) / sms;
     if (n_tokens <= 128 || waves128 * 2 < waves256 * 3) tile = 128;
     if (const char* e = getenv("SHFLBW_TILE")) { int t = atoi(e); if (t == 128 || t == 256) tile = t; }
-    if (V == 16) tile = 128;   // the only shape built for 16-row blocks
+    if constexpr (MODE != shflbw::kPanelSpmm && MODE != shflbw::kPanelConv) {
+        if (V == 16) tile = 128;   // chained layers: the only shape built for 16-row blocks
+    }
     // SpMM and chained SpConv with V = 64 / 128 can run with the operands swapped (rows in TMEM
     // lanes, one MMA per 16 columns for the whole token tile); SHFLBW_SWAP=0|1 forces the choice
     // (tuning aid).

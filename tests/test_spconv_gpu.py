@@ -123,19 +123,21 @@ def test_host_buffer_call_equals_device_call():
     assert np.array_equal(O_host.view(np.uint16), O_dev.view(np.uint16))
 
 
+@pytest.mark.parametrize("tokens", [128, 256])
 @pytest.mark.parametrize("permute", [False, True])
-def test_filter_block_height_16_on_the_tensor_cores(permute):
+def test_filter_block_height_16_on_the_tensor_cores(permute, tokens):
     """V = 16 (the reference instantiates it, spconv/blockwise_library.cu:16-32) on the tcgen05
-    kernel, at a ResNet-50 shape with batch 32 (more than 65535 output positions)."""
+    kernel (one or two 128-position accumulators per item), at a ResNet-50 shape with batch 32
+    (more than 65535 output positions)."""
     Bn, H, W, Cc, F = 32, 56, 56, 64, 64
     f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, 16, 1, 0.2, permute, 2, values="uniform")
     x = sb.uniform_half(716, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
-    O, op = run_spconv(f, Bn, H, W, 1, x)
-    assert op._state.kernel == sb.KERNEL_TCGEN05 and op._state.tokens_per_cta == 128
+    O, op = run_spconv(f, Bn, H, W, 1, x, tokens=tokens)
+    assert op._state.kernel == sb.KERNEL_TCGEN05 and op._state.tokens_per_cta == tokens
     assert_close_fp16(O, _oracle(f, Bn, H, W, 1, x), what="conv V=16")
     f2 = sb.BlockwiseSpFilter().init_random(64, 3, 3, 16, 16, 1, 0.3, True, 2, values="uniform")
     x2 = sb.uniform_half(717, 4 * 6 * 5 * 16).reshape(4, 6, 5, 16)
-    O2, _ = run_spconv(f2, 4, 6, 5, 2, x2)
+    O2, _ = run_spconv(f2, 4, 6, 5, 2, x2, tokens=tokens)
     assert_close_fp16(O2, _oracle(f2, 4, 6, 5, 2, x2), what="conv V=16 small, stride 2")
 
 

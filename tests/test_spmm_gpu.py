@@ -178,17 +178,18 @@ def test_meta_image_equals_reference_transform_and_sync_device():
     assert np.array_equal(m.meta_h, r.meta_image())
 
 
+@pytest.mark.parametrize("tokens", [128, 256])
 @pytest.mark.parametrize("permute", [False, True])
-def test_row_block_height_16_reference_shape_on_the_tensor_cores(permute):
+def test_row_block_height_16_reference_shape_on_the_tensor_cores(permute, tokens):
     """V = 16 (instantiated by the reference, spmm/blockwise_library.cu:15-31) runs on the tcgen05
-    kernel (UMMA M = 128 tokens, N = 16): the reference's own test case
-    (m,n,k,d,seed) = (1024,960,1024,0.1,2021), integer inputs, its exact acceptance rule
+    kernel (UMMA M = 128 tokens, N = 16; one or two accumulators per item): the reference's own
+    test case (m,n,k,d,seed) = (1024,960,1024,0.1,2021), integer inputs, its exact acceptance rule
     (test/test.spmm.blockwise.cu:10-14, test_util.spmm.h:18)."""
     ctypes.CDLL(None).srand(16 + permute)
     m = sb.BlockwiseSpMatrix().init_random(1024, 1024, 16, 1, 0.1, permute, 2021, values="int9")
     B = np.random.default_rng(16).integers(-4, 5, (1024, 960)).astype(np.float16)
-    D, op = run_spmm(m, 960, B)
-    assert op._state.kernel == sb.KERNEL_TCGEN05 and op._state.tokens_per_cta == 128
+    D, op = run_spmm(m, 960, B, tokens=tokens)
+    assert op._state.kernel == sb.KERNEL_TCGEN05 and op._state.tokens_per_cta == tokens
     assert oa.ref_rule_violations(D, _oracle(m, 960, B)) == 0
 
 
