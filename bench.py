@@ -146,7 +146,11 @@ class Dist:
         torch.cuda.set_device(self.local)
         if self.world > 1:
             import torch.distributed as dist
-            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            # a rendezvous or collective that does not complete ends the run with an error after three
+            # minutes instead of the default ten
+            import datetime
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local),
+                                    timeout=datetime.timedelta(seconds=180))
             self.pg = dist
 
     def barrier(self):
