@@ -95,6 +95,12 @@ struct alignas(64) PanelParams {
     float alpha, beta;
     int num_items, tiles_n;  // work items = row blocks x token tiles; item -> (item / tiles_n, item % tiles_n)
     FastDiv div_tiles, div_bp, div_wo;   // division by tiles_n, Bp, Wo (set by the host with make_fast_div)
+    // Order of the work items.  0: item = block * tiles_n + tile (a CTA's neighbours work on the
+    // same row block).  1: item = tile * num_blocks + block: the CTAs that run at the same time
+    // share a few token tiles, so the rows of the dense operand they gather are a small set that
+    // stays in L2 (SpMM with a large dense operand).
+    int tile_major, num_blocks;
+    FastDiv div_blocks;
     unsigned long long* trace;  // tuning builds only: per-role timestamps of CTA 0
     int inject_from;         // fault-injection builds only (-DSHFLBW_FAULT_INJECT): from this stage number on, one
                              // producer warp withholds its arrivals, so the consumer's bounded wait runs out (< 0: off)
@@ -277,6 +283,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
 #endif
     // This CTA's work items: blockIdx.x, blockIdx.x + gridDim.x, ...  (host guarantees nloc <= table size)
     const int nloc = (p.num_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+    auto item_block = [&](int item) { return p.tile_major ? item - fast_div(item, p.div_blocks) * p.num_blocks : fast_div(item, p.div_tiles); };
+    auto item_tile = [&](int item) { return p.tile_major ? fast_div(item, p.div_blocks) : item - fast_div(item, p.div_tiles) * p.tiles_n; };
 
     if (tid == 0) CTRACE(0);
     if (tid == 0) {
@@ -299,7 +307,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         sm100::mbar_init_fence();
     }
     for (int li = tid; li < nloc; li += blockDim.x) {
-        const int blk = fast_div((int)blockIdx.x + li * (int)gridDim.x, p.div_tiles);
+        const int blk = item_block((int)blockIdx.x + li * (int)gridDim.x);
         const int b0 = __ldg(p.blk_ptr + blk);
         item_tab[li] = make_int2(b0, __ldg(p.blk_ptr + blk + 1) - b0);
     }
@@ -381,7 +389,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const int num_k = (ent.y + KS - 1) / KS;
             if (num_k == 0) continue;
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int col = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T + cbox * 64;     // first token of this lane's box (beyond N: zero fill)
+            const int col = item_tile(item) * T + cbox * 64;     // first token of this lane's box (beyond N: zero fill)
             const __half* wsrc = p.blk_val + (size_t)ent.x * V;
             for (int kt = 0; kt < num_k; ++kt, ++it) {
                 if ((it % GROUPS) != grp) continue;
@@ -491,7 +499,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const int num_k = (ent.y + KS - 1) / KS;
             if (num_k == 0) continue;
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int tok0 = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T + chunk * 8;
+            const int tok0 = item_tile(item) * T + chunk * 8;
             const bool chunk_ok = tok0 < p.N;
             const uint32_t nbytes = chunk_ok ? 16u : 0u;
             const __half* conv_src0 = p.Xs;
@@ -645,7 +653,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             if (num_k == 0) continue;
             // per-item decode of this lane's tokens
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int tok0 = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T + chunk * 8;
+            const int tok0 = item_tile(item) * T + chunk * 8;
             const bool chunk_ok = tok0 < p.N;
             const uint32_t nbytes = chunk_ok ? 16u : 0u;
             // SpConv: this lane's 8 tokens are 8 images of one output pixel; the staged input
@@ -911,8 +919,8 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
             const long long ew0 = clock64();
 #endif
             const int item = (int)blockIdx.x + li * (int)gridDim.x;
-            const int blk = fast_div(item, p.div_tiles);
-            const int n0 = (item - fast_div(item, p.div_tiles) * p.tiles_n) * T;
+            const int blk = item_block(item);
+            const int n0 = item_tile(item) * T;
             const bool has_k = item_tab[li].y > 0 && !(ablate & 1);
             const int b = li % NBUF;
             // Wait for the item's accumulator (one lane polls, the warp follows).  false: the wait

@@ -527,6 +527,11 @@ int shflbw_spmm_exec(const shflbw_spmm_state_t* st, void* stream) {
         if (st->gather == shflbw::kGatherTma) std::memcpy(p.tmap_b, st->tmap_b, sizeof p.tmap_b);
         p.num_items = st->num_items; p.tiles_n = st->tiles_n;
         p.div_tiles = shflbw::make_fast_div(st->tiles_n); p.div_bp = p.div_wo = shflbw::make_fast_div(1);
+        // Tile-major item order: concurrent CTAs gather from the same few token tiles of B (SHFLBW_ITEM_ORDER=0|1
+        // forces block-major / tile-major; tuning aid).
+        p.num_blocks = st->num_row_blocks; p.div_blocks = shflbw::make_fast_div(st->num_row_blocks);
+        p.tile_major = 1;
+        if (const char* e = getenv("SHFLBW_ITEM_ORDER")) p.tile_major = atoi(e) != 0;
 #if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
         if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
         if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
@@ -787,6 +792,12 @@ int shflbw_spconv_exec(const shflbw_spconv_state_t* st, void* stream) {
     p.R = st->R; p.S = st->S; p.stride = st->stride; p.Ho = st->Ho; p.Wo = st->Wo;
     p.num_items = st->num_items; p.tiles_n = st->tiles_n;
     p.div_tiles = shflbw::make_fast_div(st->tiles_n); p.div_bp = shflbw::make_fast_div(st->Bp); p.div_wo = shflbw::make_fast_div(st->Wo);
+    p.num_blocks = st->F / st->V; p.div_blocks = shflbw::make_fast_div(p.num_blocks);
+    // Block-major item order for the convolutions: running a token tile's filter blocks at the same time
+    // (tile-major) was measured equal on the ResNet-50 stack and on config 3, whose inputs are small next
+    // to their outputs (SHFLBW_ITEM_ORDER=1 forces tile-major; tuning aid).
+    p.tile_major = 0;
+    if (const char* e = getenv("SHFLBW_ITEM_ORDER")) p.tile_major = atoi(e) != 0;
 #if defined(SHFLBW_ABLATE) || defined(SHFLBW_COUNTERS)
     if (const char* e = getenv("SHFLBW_ABLATE")) p.ablate = atoi(e);
     if (const char* e = getenv("SHFLBW_TRACE_PTR")) p.trace = (unsigned long long*)strtoull(e, nullptr, 0);
