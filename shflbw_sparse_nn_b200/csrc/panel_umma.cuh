@@ -21,22 +21,26 @@
 // The description below is written for the first orientation; the second differs in the
 // gathered tile's layout ([K group][T/64 swizzle atoms]), the MMA issue and the epilogue.
 //
-// One CTA per SM loops over items (item = blockIdx.x + i*gridDim.x); their extents are read
-// once into a shared-memory table.  Warp roles (warp w issues from scheduler partition w % 4):
-//   warps 0-7        epilogue: TMEM -> registers -> fp16 -> 32x32 transpose in shared memory ->
-//                    16-byte global stores (inverse row permutation fused for SpMM); warp w
-//                    reads TMEM lane quadrant w % 4, column half w / 4
-//   warp  8          allocates TMEM; its lane 0 issues tcgen05.mma, releases stages and
+// One CTA per SM loops over items (item = blockIdx.x + i*gridDim.x, decoded block-major or
+// tile-major, PanelParams::tile_major); their extents are read once into a shared-memory table.
+// Warp roles (warp w issues from scheduler partition w % 4; EW = 8 or 16 epilogue warps):
+//   warps 0..EW-1    epilogue.  Warp w reads TMEM lane quadrant w % 4 and part w / 4 of the
+//                    accumulator columns.  Tokens in lanes: TMEM -> registers -> fp16 -> transpose
+//                    of 32-row chunks through shared memory -> 16-byte global stores (inverse row
+//                    permutation fused for SpMM).  Rows in lanes: stores straight from registers.
+//   warp  EW         allocates TMEM; its lane 0 issues tcgen05.mma, releases stages and
 //                    accumulators with tcgen05.commit
-//   warps 9.. with w % 4 != 0   producers (PW of them, in two groups that take the stages in
-//                    turn): 16-byte cp.async gathers into 128-byte-swizzled stages, one bulk
-//                    copy per stage for the value slice.  A group publishes its previous stage
-//                    half-way through issuing the next one, with ONE mbarrier arrival per warp.
-//                    Row ids are prefetched two of the group's stages ahead by 4-byte cp.async
-//                    into a shared-memory ring.
-//   warps 12, 16     idle, so that no producer shares the MMA warp's scheduler partition.
-// The accumulator is double buffered in TMEM so the epilogue of item i overlaps the main
-// loop of item i+1, and the stage ring runs across item boundaries without draining.
+//   warps EW+1.. with w % 4 != 0   producers (PW of them, in GROUPS groups that take the stages in
+//                    turn).  cp.async gather: 16-byte copies into 128-byte-swizzled stages; a
+//                    group publishes its previous stage half-way through issuing the next one,
+//                    with ONE mbarrier arrival per warp; row ids are prefetched LAG+1 of the
+//                    group's stages ahead by 4-byte cp.async into a shared-memory ring.  TMA
+//                    gather: one tile::gather4 per lane, completion by byte count.  One bulk copy
+//                    per stage for the value slice either way.
+//   later warps with w % 4 == 0   idle, so that no producer shares the MMA warp's scheduler partition.
+// The accumulator is double buffered in TMEM (four sets with EW = 16) so the epilogue of item i
+// overlaps the main loop of item i+1, and the stage ring runs across item boundaries without
+// draining.
 //
 // Every mbarrier wait is bounded (sm100_ptx.cuh): on a timeout the kernel records a code in
 // the status word, raises a CTA-wide abort flag, drains and exits; it cannot hang the GPU.
