@@ -82,6 +82,17 @@ def ncu_traffic():
         return None, None
 
 
+def ncu_spconv_shares():
+    """Share of each of the three launches of an NHWC SpConv call (planes-out plan) in the call's
+    device time, from the ncu launch list summarised under profiles/ (cold-cache, serialised);
+    None when no record is there."""
+    p = ROOT / "profiles" / "panel_umma_spconv_16x14x14x512.json"
+    try:
+        return json.loads(p.read_text())["share_of_the_call"]
+    except Exception:
+        return None
+
+
 def spmm_bytes(nnzb, V, X, M, K_touched, N, permuted=True):
     """Compulsory bytes of one SpMM: values + indices + indptr + permutation + B once + D once."""
     return 2 * nnzb * V + 4 * nnzb + 4 * (X + 1) + (4 * M if permuted else 0) + 2 * K_touched * N + 2 * M * N
@@ -437,7 +448,8 @@ def bench_spconv(sb, torch, dist, pk, steps=300, warmup=20, use_graph=True):
             "launches_per_call": ops[0].launches_per_exec,
             "plan": "planes out (filters in TMEM lanes) + transpose" if st.variant == 1 else "positions out (tokens in TMEM lanes)",
             "launch": (f"CUDA graph of {G} calls" if G else "host launches"), "repeats": R,
-            "t_roof_us": round(t_roof * 1e6, 3), "roofline_frac": round(t_roof / t, 4), "algorithmic_bytes": byt, "nnzb": f.nnzb}
+            "t_roof_us": round(t_roof * 1e6, 3), "roofline_frac": round(t_roof / t, 4), "algorithmic_bytes": byt, "nnzb": f.nnzb,
+            "launch_shares_ncu": ncu_spconv_shares() if st.variant == 1 else None}
 
 
 def bench_resnet50(torch, dist):
