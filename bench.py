@@ -157,8 +157,12 @@ class Dist:
         torch.cuda.set_device(self.local)
         if self.world > 1:
             import torch.distributed as dist
-            # a rendezvous or collective that does not complete ends the run with an error after three
-            # minutes instead of the default ten
+            # The collectives here are a barrier, a max over a few doubles and one optional all-gather:
+            # nothing that needs in-switch reduction, so NCCL's NVLink-multicast set-up is left out
+            # unless the caller asks for it (one 4-GPU run on a shared box never got past NCCL's
+            # initialisation).  A rendezvous or collective that does not complete ends the run with
+            # an error after three minutes instead of the default ten.
+            os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
             import datetime
             dist.init_process_group("nccl", device_id=torch.device("cuda", self.local),
                                     timeout=datetime.timedelta(seconds=180))
