@@ -329,7 +329,10 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
     // the stream; the dense operand, the residual and the output are touched only below.  The
     // next kernel may start its own prologue as soon as every block of this one got here.
     sm100::grid_dependency_launch();
-    sm100::grid_dependency_wait();
+    // The wait itself is executed per role, as late as each role allows: by the producers after
+    // their first row ids (sparse operand) are on their way and before their first gather, by the
+    // epilogue warps at once (they read C / the residual and write the output); the MMA warp
+    // touches no global memory and does not wait.
     if (tid == 0) TRACE(3, 0, 0);
     if (tid == 0) CTRACE(1);
 
@@ -384,6 +387,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         for (int g = 0; g < GROUPS; ++g) advance(pre);
         int4 ids_next = load_ids(pre);                       // and its second: two stages of ids are in flight,
         for (int g = 0; g < GROUPS; ++g) advance(pre);       // which covers the load's latency even with one group
+        sm100::grid_dependency_wait();                       // the dense operand may be the previous kernel's output
         int it = 0;
 #ifdef SHFLBW_COUNTERS
         long long pc_empty = 0, pc_n = 0, pc_t0 = clock64();
@@ -494,6 +498,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         for (int g = 0; g < GROUPS; ++g) advance(pre);
         int id_next = load_id(pre);
         for (int g = 0; g < GROUPS; ++g) advance(pre);
+        sm100::grid_dependency_wait();                       // the dense operand may be the previous kernel's output
         int it = 0;
 #ifdef SHFLBW_COUNTERS
         long long pc_empty = 0, pc_n = 0, pc_t0 = clock64();
@@ -643,6 +648,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         sm100::cp_async_commit();
         sm100::cp_async_wait<0>();
         __syncwarp();
+        sm100::grid_dependency_wait();                         // the dense operand may be the previous kernel's output
 
         int it = 0;        // stage counter across items (all groups count the same sequence)
         int pend[LAG];     // this group's stages not yet published, oldest first
@@ -907,6 +913,7 @@ panel_umma_kernel(const __grid_constant__ PanelParams p) {
         // Warp w reads TMEM lane quadrant w % 4 (tokens) and part w / 4 of the accumulator
         // columns (the block's output rows / filters): halves with eight warps, quarters with
         // sixteen.
+        sm100::grid_dependency_wait();
         const int quad = warp & 3, half_id = warp >> 2;
         // (a single 16- or 32-column accumulator is not split; two 16-column accumulators go to the two halves)
         constexpr int HALVES = (Cfg::ACC_COLS >= 64 || (V == 16 && TM == 2)) ? EW / 4 : 1;
