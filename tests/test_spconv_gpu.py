@@ -183,3 +183,18 @@ def test_host_buffer_call_pipelines_large_batches_in_chunks():
     sb.spconv_host(f, Bn, H, W, 1, x, out, alpha=0.5)
     f.device_status()
     assert_close_fp16(out, _oracle(f, Bn, H, W, 1, x, 0.5), what="chunked host conv")
+
+
+def test_both_work_item_orders_give_the_same_bits(monkeypatch):
+    """SpConv decodes its work items block-major by default; the tile-major order (an override) must
+    give the same output bits."""
+    Bn, H, W, Cc, F, V = 8, 14, 14, 64, 256, 64
+    f = sb.BlockwiseSpFilter().init_random(F, 3, 3, Cc, V, 1, 0.2, True, 9, values="uniform")
+    x = sb.uniform_half(10, Bn * H * W * Cc).reshape(Bn, H, W, Cc)
+    out = {}
+    for order in ("0", "1"):
+        monkeypatch.setenv("SHFLBW_ITEM_ORDER", order)
+        out[order], _ = run_spconv(f, Bn, H, W, 1, x)
+    assert_close_fp16(out["1"], _oracle(f, Bn, H, W, 1, x), what="tile-major conv")
+    assert np.array_equal(out["0"].view(np.uint16), out["1"].view(np.uint16))
+

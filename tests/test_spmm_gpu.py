@@ -317,3 +317,20 @@ def test_tma_tile_gather_kernel(N, monkeypatch):
     assert_close_fp16(D2, _oracle(m, N, B, 0.5, Cm, -1.5), what=f"TMA gather N={N} alpha/beta")
     assert np.array_equal(D1.view(np.uint16), E1.view(np.uint16)) and np.array_equal(D2.view(np.uint16), E2.view(np.uint16))
 
+
+@pytest.mark.parametrize("V,swap", [(64, 1), (64, 0), (128, 1), (32, 0)])
+def test_both_work_item_orders_give_the_same_bits(V, swap, monkeypatch):
+    """Work items are decoded block-major (item = block * tiles + tile) or tile-major (item = tile *
+    blocks + block, the SpMM default: concurrent CTAs share a few token tiles of B).  Every item is
+    computed by one CTA in the same order of additions either way, so the outputs are identical."""
+    M, K, N = 6 * V, 512, 1160
+    m = sb.BlockwiseSpMatrix().init_random(M, K, V, 1, 0.3, True, 61 + V, values="uniform")
+    B = sb.uniform_half(62, K * N).reshape(K, N)
+    out = {}
+    for order in ("0", "1"):
+        monkeypatch.setenv("SHFLBW_ITEM_ORDER", order)
+        with operand_swap(swap):
+            out[order], _ = run_spmm(m, N, B, alpha=0.5)
+    assert_close_fp16(out["1"], _oracle(m, N, B, 0.5), what=f"tile-major V={V}")
+    assert np.array_equal(out["0"].view(np.uint16), out["1"].view(np.uint16))
+
